@@ -1,6 +1,6 @@
 // common.cuh -- device helpers for the sm_100a compressed-KV kernels:
 // bf16 rounding, the bit-reproducible exp / dot definitions shared with the test oracle's
-// restatement, mbarrier + TMA bulk copies (UBLKCP), cluster barriers and DSMEM stores.
+// restatement, mbarrier + TMA bulk copies, cluster barriers and DSMEM stores.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -131,7 +131,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity) {
         "DONE_%=:\n"
         "}\n" :: "r"(smem_u32(bar)), "r"(parity) : "memory");
 }
-// 1-D bulk copy global -> this CTA's shared memory through the TMA engine (SASS: UBLKCP).
+// 1-D bulk copy global -> this CTA's shared memory through the TMA engine.
 // dst and src 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void tma_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
     asm volatile(

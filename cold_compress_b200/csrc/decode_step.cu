@@ -12,7 +12,7 @@
 //     are cut into chunks of CH rows (16/32/64) dealt round-robin to the CTAs of the cluster, so
 //     a head whose live slots are a prefix (hybrid, caches still filling) stays balanced
 //     -> Hkv*C CTAs (128 of 148 SMs for Llama-3-8B);
-//   * the K and V rows of each chunk are streamed by the TMA engine (cp.async.bulk, UBLKCP) into
+//   * the K and V rows of each chunk are streamed by the TMA engine (cp.async.bulk) into
 //     a shared-memory ring, as many chunks in flight as the ring holds from the first instruction;
 //   * three DSMEM all-to-all exchanges per step: {arg-min candidate, row max}, {softmax sum},
 //     {P.V partials}; the first one carries both the eviction decision and the softmax max, so

@@ -8,7 +8,7 @@
 //
 //   * one CTA per SM (cooperative launch: all co-resident), 8 warps; the rows of every stage are dealt to CTAs and,
 //     inside a CTA, to warps, statically;
-//   * every warp owns a private ring of 8 KiB shared-memory stages fed by the TMA engine (cp.async.bulk, UBLKCP):
+//   * every warp owns a private ring of 8 KiB shared-memory stages fed by the TMA engine (cp.async.bulk):
 //     the moment a warp has consumed a stage it re-arms it with the NEXT tile of its own static tile sequence --
 //     the sequence runs across stage boundaries (weights of wo / w1 / w3 / w2 / the next layer, this layer's K/V
 //     rows), so up to ~190 KiB per SM are in flight or resident while the warp waits for a predecessor stage;
