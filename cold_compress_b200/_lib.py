@@ -130,3 +130,59 @@ def check(rc: int, what: str = "") -> int:
     if rc < 0:
         raise CcError(f"{what or 'cc call'} failed ({rc}): {load().cc_last_error().decode()}")
     return rc
+
+
+# --------------------------------------------------------------------------- libcc_b200_seq.so (include/cc_b200_seq.h)
+SEQ_SO_PATH = Path(os.environ.get("CC_B200_SEQ_LIB", PKG / "libcc_b200_seq.so"))
+SEQ_ABI_VERSION = 1
+DT_F32, DT_BF16 = 0, 1
+SINK_NONE, SINK_LEARNED, SINK_ZERO = 0, 1, 2
+
+
+class CcSeqAttn(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("q", "k_new", "v_new", "k_cache", "v_cache", "pos", "mask", "cache_cts",
+                                          "input_pos", "y", "sink")] + [
+        (n, C.c_int32) for n in ("T", "H", "G", "Dk", "Dv", "L", "window", "sink_mode", "cache_dtype", "y_dtype")] + [
+        ("scale", C.c_float), ("append", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64)]
+
+
+_i32, _f32, _vp = C.c_int32, C.c_float, C.c_void_p
+SEQ_EXPORTS = {
+    "cc_seq_abi_version": (C.c_int, []),
+    "cc_seq_last_error": (C.c_char_p, []),
+    "cc_seq_embed": (C.c_int, [_vp] * 8 + [_i32, _i32, _f32, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "cc_seq_qkv_prepare": (C.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32,
+                                     _f32, _i32, _f32, _i32, _vp]),
+    "cc_seq_attention": (C.c_int, [C.POINTER(CcSeqAttn), _vp]),
+    "cc_seq_attention_decode": (C.c_int, [C.POINTER(CcSeqAttn), _vp]),
+    "cc_seq_decode_workspace": (C.c_uint64, [_i32] * 5),
+    "cc_seq_cache_append": (C.c_int, [C.POINTER(CcSeqAttn), _vp]),
+    "cc_seq_residual_norm": (C.c_int, [_vp, _vp, _i32, _vp, _f32, _f32, _vp, _i32, _i32, _i32, _vp]),
+    "cc_seq_clamped_glu": (C.c_int, [_vp, _vp, _i32, _i32, _f32, _f32, _i32, _i32, _vp]),
+}
+
+_seq_lib = None
+
+
+def load_seq() -> C.CDLL:
+    """Load the sequence-kernel library; raises if it has not been built (python -m cold_compress_b200.build)."""
+    global _seq_lib
+    if _seq_lib is not None:
+        return _seq_lib
+    if not SEQ_SO_PATH.exists():
+        raise CcError(f"{SEQ_SO_PATH} is missing: build it with `python -m cold_compress_b200.build --only=seq` "
+                      "(nvcc, sm_100a). There is no CPU or PyTorch fallback for these kernels.")
+    lib = C.CDLL(str(SEQ_SO_PATH))
+    for name, (restype, argtypes) in SEQ_EXPORTS.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = restype, argtypes
+    if lib.cc_seq_abi_version() != SEQ_ABI_VERSION:
+        raise CcError(f"ABI mismatch: library {lib.cc_seq_abi_version()} vs binding {SEQ_ABI_VERSION}")
+    _seq_lib = lib
+    return lib
+
+
+def check_seq(rc: int, what: str = "") -> int:
+    if rc < 0:
+        raise CcError(f"{what or 'cc_seq call'} failed ({rc}): {load_seq().cc_seq_last_error().decode()}")
+    return rc

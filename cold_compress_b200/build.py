@@ -1,8 +1,10 @@
-"""Builds libcc_b200.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
+"""Builds the C-ABI CUDA libraries in-tree with nvcc for sm_100a.
 
-    python -m cold_compress_b200.build [--force]
+    python -m cold_compress_b200.build [--force] [--only=core|seq]
 
-The built .so is git-ignored but travels to the GPU box with the gpurun snapshot.
+`core` = libcc_b200.so (csrc/*.cu: the compressed-KV decode path), `seq` = libcc_b200_seq.so (csrc/seq/*.cu: the
+position-addressed sequence kernels).  Each library is built on its own, so a model that needs one of them does not
+wait for the other.  The built .so files are git-ignored but travel to the GPU box with the gpurun snapshot.
 """
 from __future__ import annotations
 
@@ -19,8 +21,47 @@ NVCC_FLAGS = [*(["-DCC_TOKEN_MICROTRACE"] if __import__("os").environ.get("CC_TO
               "--shared", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
 
+SEQ_SO = PKG / "libcc_b200_seq.so"
+SEQ_HEADER = PKG.parent / "include" / "cc_b200_seq.h"
+
+
 def sources():
     return sorted(CSRC.glob("*.cu"))
+
+
+def seq_sources():
+    return sorted((CSRC / "seq").glob("*.cu"))
+
+
+def seq_needs_build() -> bool:
+    if not SEQ_SO.exists():
+        return True
+    newest = max(p.stat().st_mtime for p in seq_sources() + [SEQ_HEADER])
+    return SEQ_SO.stat().st_mtime < newest
+
+
+def build_seq_extension(force: bool = False, verbose: bool = False) -> Path:
+    """csrc/seq/*.cu -> libcc_b200_seq.so.  Safe when several processes start at once: the library is linked under a
+    temporary name and renamed into place."""
+    if not force and not seq_needs_build():
+        return SEQ_SO
+    import os
+    import tempfile
+    flags = [f for f in NVCC_FLAGS if f != "-Xptxas" and f != "-v"]
+    fd, tmp = tempfile.mkstemp(dir=str(PKG), prefix=".libcc_b200_seq.", suffix=".so")
+    os.close(fd)
+    try:
+        res = subprocess.run(["nvcc", *flags, "-o", tmp, *[str(s) for s in seq_sources()]], capture_output=True, text=True)
+        if verbose or res.returncode:
+            sys.stderr.write(res.stdout + res.stderr)
+        if res.returncode:
+            raise RuntimeError("nvcc failed building libcc_b200_seq.so")
+        os.chmod(tmp, 0o755)
+        os.replace(tmp, SEQ_SO)
+    finally:
+        if os.path.exists(tmp):
+            os.unlink(tmp)
+    return SEQ_SO
 
 
 def needs_build() -> bool:
@@ -74,4 +115,8 @@ def build_extension(force: bool = False, verbose: bool = False, out: Path | None
 
 if __name__ == "__main__":
     out = next((a.split("=", 1)[1] for a in sys.argv if a.startswith("--out=")), None)
-    print(build_extension(force="--force" in sys.argv, verbose="--quiet" not in sys.argv, out=out))
+    only = next((a.split("=", 1)[1] for a in sys.argv if a.startswith("--only=")), None)
+    if only in (None, "core"):
+        print(build_extension(force="--force" in sys.argv, verbose="--quiet" not in sys.argv, out=out))
+    if only in (None, "seq"):
+        print(build_seq_extension(force="--force" in sys.argv, verbose="--quiet" not in sys.argv))

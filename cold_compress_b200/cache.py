@@ -101,8 +101,10 @@ class KVCache(nn.Module):
         self.head_specific, self.variable_length = head_specific, variable_length
         L = self.max_cache_length
         self.cache_shape = (max_batch_size, n_heads, L, head_dim)
+        # value rows may be narrower or wider than key rows (v_head_dim kwarg); the eviction kernels need them equal
+        self.v_head_dim = int(getattr(self, "v_head_dim", None) or head_dim)
         self.register_buffer("k_cache", torch.zeros(self.cache_shape, dtype=dtype))
-        self.register_buffer("v_cache", torch.zeros(self.cache_shape, dtype=dtype))
+        self.register_buffer("v_cache", torch.zeros((max_batch_size, n_heads, L, self.v_head_dim), dtype=dtype))
         self.register_buffer("pos", torch.full((max_batch_size, n_heads if head_specific else 1, L), -1, dtype=torch.int))
         self.register_buffer("cache_cts", torch.zeros(n_heads if variable_length else 1, dtype=torch.int))
         self.register_buffer("mask", torch.zeros((max_batch_size, n_heads, 1, L), dtype=torch.bool))
@@ -222,7 +224,47 @@ class KVCache(nn.Module):
     def _external_fill_idx(self, input_pos):
         raise NotImplementedError
 
+    # ---- position-addressed step (sequence kernels, csrc/seq) ------------------------------------
+    def sequence_window(self):
+        """How many positions back a slot survives when tokens are appended in order (slot = position mod L), or
+        None when this cache's policy does not keep a contiguous run of positions."""
+        return None
+
+    def sequence_step(self, q, k_new, v_new, input_pos, y, window=0, sink=None, sink_mode=0, scale=1.0):
+        """Attention of T consecutive new tokens over the cache and themselves, then their append, with every key
+        addressed by position: q [T, Hq, Dk] fp32 (normalised), k_new [T, H, Dk] / v_new [T, H, Dv] in the cache's
+        dtype, input_pos int32 [1] = position of the first token (device), y [T, Hq, Dv] out.  Query p sees key j
+        when j <= p and (window == 0 or p - j < window).  T == 1 is one launch (keys split over CTAs, append fused);
+        T > 1 is the tiled chunk kernel followed by the append kernel.  Nothing here synchronises with the host."""
+        from . import seq_ops
+        keep = self.sequence_window()
+        if keep is None or self.quantize:
+            raise _lib.CcError(f"{type(self).__name__} cannot serve position-addressed steps")
+        if (window == 0 and keep != 0) or (window > 0 and keep != 0 and keep < window):
+            raise _lib.CcError(f"cache keeps {keep} positions but the layer looks back {window or 'without limit'}")
+        T = q.shape[0]
+        args = (q, k_new, v_new, self.k_cache, self.v_cache, self.pos, self.mask, self.cache_cts, input_pos, y, sink,
+                int(window), int(sink_mode), float(scale))
+        if T == 1:
+            seq_ops.seq_attention(*args, seq_ops.ATTN_DECODE_APPEND, self._sequence_workspace(q.shape[1], window))
+        else:
+            seq_ops.seq_attention(*args, seq_ops.ATTN_CHUNK, None)
+            seq_ops.seq_attention(*args, seq_ops.ATTN_APPEND_ONLY, None)
+        return y
+
+    def _sequence_workspace(self, n_q_heads, window):
+        from . import seq_ops
+        key = (n_q_heads, int(window), self.k_cache.device)
+        ws = self._out.get("seq_ws")
+        if ws is None or ws[0] != key:
+            nbytes = seq_ops.decode_workspace_bytes(n_q_heads, self.n_heads, self.v_head_dim, self.max_cache_length, int(window))
+            ws = (key, torch.zeros((nbytes + 3) // 4, dtype=torch.int32, device=self.k_cache.device))
+            self._out["seq_ws"] = ws
+        return ws[1]
+
     def _launch(self, phases, q, k_val, v_val, input_pos, probs_in=None, **kwargs):
+        if self.v_head_dim != self.head_dim:
+            raise _lib.CcError("the eviction kernels need value rows as wide as key rows")
         dev = self.k_cache.device
         if dev.type != "cuda":
             raise _lib.CcError("the compressed-KV decode path is CUDA-only: move the model to a B200 (no CPU fallback)")
@@ -304,6 +346,9 @@ class KVCacheFull(KVCacheHeadConstant):
     def _external_fill_idx(self, input_pos):
         return self.pos[0, 0].argmin().view(1)  # first unfilled slot (reference cache.py:500-502)
 
+    def sequence_window(self):
+        return 0  # nothing is ever evicted: slot = position while the sequence fits
+
 
 class KVCacheRandom(KVCacheHeadConstant):
     relevant_kwargs = ["max_cache_length", "max_seq_length", "cache_bits", "global_tokens", "recent_window"]
@@ -331,6 +376,10 @@ class KVCacheRecentGlobal(KVCacheHeadConstant):
     """Sliding window + global tokens; the window is max_cache_length - global_tokens (reference cache.py:527-556)."""
     relevant_kwargs = ["max_cache_length", "max_seq_length", "cache_bits", "global_tokens"]
     policy = _lib.POLICY_RECENT_GLOBAL
+
+    def sequence_window(self):
+        # without global tokens the policy is a ring over the last L positions
+        return self.max_cache_length if not self.global_tokens else None
 
 
 class KVCacheL2(KVCacheHeadSpecific):

@@ -1,0 +1,620 @@
+// seq_kernels.cu -- position-addressed sequence kernels behind include/cc_b200_seq.h (libcc_b200_seq.so).
+//
+// Arithmetic rule of this file: positions, angles, norms, attention scores, softmax weights, the weighted value sum
+// and the residual stream are fp32 whatever the storage type of activations, weights and cache rows (fp32 or bf16);
+// expf / logf / sinf / cosf / sqrtf are the accurate versions (no fast-math).  Results of the attention kernels depend on
+// the key positions a query sees, never on which launch, chunk or slot brought a key: keys are addressed by
+// position (slot = position mod capacity, checked against the slot's recorded position).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../../include/cc_b200_seq.h"
+
+namespace ccs {
+
+static thread_local char g_err[512] = "";
+static int fail(int code, const char* msg) {
+    strncpy(g_err, msg, sizeof(g_err) - 1);
+    g_err[sizeof(g_err) - 1] = 0;
+    return code;
+}
+static int cuda_check(const char* where) {
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return CC_SEQ_OK;
+    snprintf(g_err, sizeof(g_err), "%s: %s", where, cudaGetErrorString(e));
+    return CC_SEQ_ERR_CUDA;
+}
+
+__device__ __forceinline__ float ldf(const float* p, size_t i) { return p[i]; }
+__device__ __forceinline__ float ldf(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void stf(float* p, size_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ------------------------------------------------------------------------------------------------ embedding
+template <typename WT, typename AT>
+__global__ void embed_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ input_pos,
+                             int32_t* prev_token, const WT* __restrict__ embed, const WT* __restrict__ bigram,
+                             const float* __restrict__ inv_freq, float* __restrict__ x, AT* __restrict__ x_act, int T,
+                             int E, float scale, int buckets, int mul_prev, int mul_cur) {
+    const int t = blockIdx.x;
+    const int p = input_pos[0] + t;
+    const int tok = tokens[t];
+    long long row = -1;
+    if (bigram != nullptr) {
+        if (p == 0) {
+            row = buckets;
+        } else {
+            const long long prev = t > 0 ? tokens[t - 1] : prev_token[0];
+            row = (prev * (long long)mul_prev + (long long)tok * (long long)mul_cur) % (long long)buckets;
+            if (row < 0) row += buckets;
+        }
+    }
+    const float pf = (float)p;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        float v = ldf(embed, (size_t)tok * E + e) * scale;
+        if (row >= 0) v += ldf(bigram, (size_t)row * E + e);
+        const float ang = pf * inv_freq[e >> 1];
+        v += (e & 1) ? cosf(ang) : sinf(ang);
+        x[(size_t)t * E + e] = v;
+        if (x_act != nullptr) stf(x_act, (size_t)t * E + e, v);
+    }
+    if (t == 0) {  // every thread of this block has read the old state above
+        __syncthreads();
+        if (threadIdx.x == 0) prev_token[0] = tokens[T - 1];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ q/k/v preparation
+template <typename IT, typename OT>
+__global__ void qkv_prepare_kernel(const IT* __restrict__ qkv, const float* __restrict__ bias,
+                                   const int32_t* __restrict__ input_pos, const float* __restrict__ mix_lambda,
+                                   const OT* __restrict__ v_first, float* __restrict__ q_out, OT* __restrict__ k_out,
+                                   OT* __restrict__ v_out, int T, int H, int G, int Dk, int Dv, float eps, int unit_norm,
+                                   float gain_coef, int gain_every) {
+    const int t = blockIdx.x;
+    const int N = (H + G) * Dk + G * Dv;
+    const IT* row = qkv + (size_t)t * N;
+    const int p = input_pos[0] + t;
+    float gain = 1.0f;
+    if (gain_every > 0) gain = 1.0f + gain_coef * logf((float)((p + 1) / gain_every + 1));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    for (int hh = warp; hh < H + G; hh += nwarp) {
+        const int off = hh * Dk;
+        float ss = 0.f;
+        for (int d = lane; d < Dk; d += 32) {
+            float v = ldf(row, off + d);
+            if (bias != nullptr) v += bias[off + d];
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+        const float r = unit_norm ? 1.0f / sqrtf(ss / (float)Dk + eps) : 1.0f;
+        for (int d = lane; d < Dk; d += 32) {
+            float v = ldf(row, off + d);
+            if (bias != nullptr) v += bias[off + d];
+            if (hh < H) q_out[((size_t)t * H + hh) * Dk + d] = v * r * gain;
+            else stf(k_out, ((size_t)t * G + (hh - H)) * Dk + d, v * r);
+        }
+    }
+    const int voff = (H + G) * Dk, NV = G * Dv;
+    const float lam = v_first != nullptr ? mix_lambda[0] : 0.f;
+    for (int i = threadIdx.x; i < NV; i += blockDim.x) {
+        float v = ldf(row, voff + i);
+        if (bias != nullptr) v += bias[voff + i];
+        if (v_first != nullptr) v = (1.0f - lam) * v + lam * ldf(v_first, (size_t)t * NV + i);
+        stf(v_out, (size_t)t * NV + i, v);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ chunk attention
+constexpr int BQ = 64, BK = 64, ATT_THREADS = 256;
+
+__device__ __forceinline__ int key_source(const CcSeqAttn& a, int j, int p0) {
+    // >= 0: cache slot, -1: not a key, <= -2: row -(s + 2) of the chunk
+    if (j >= p0) return -(j - p0) - 2;
+    const int slot = j % a.L;
+    return a.pos[slot] == j ? slot : -1;
+}
+
+template <typename CT, typename YT, int DVT>
+__global__ void __launch_bounds__(ATT_THREADS) attn_chunk_kernel(const CcSeqAttn a) {
+    extern __shared__ float sm[];
+    const int Dk = a.Dk, Dv = a.Dv, Dkp = Dk | 1;
+    constexpr int DVW = 16 * DVT, SP = BK + 1;
+    float* Qs = sm;
+    float* Ks = Qs + BQ * Dkp;
+    float* Vs = Ks + BK * Dkp;
+    float* Ss = Vs + BK * DVW;
+    int* ksrc = (int*)(Ss + BQ * SP);
+
+    const int qb = blockIdx.x, h = blockIdx.y, g = h / (a.H / a.G);
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int p0 = a.input_pos[0];
+    const int i0 = qb * BQ;
+    const int nq = min(BQ, a.T - i0);
+    const CT* kc = (const CT*)a.k_cache;
+    const CT* vc = (const CT*)a.v_cache;
+    const CT* kn = (const CT*)a.k_new;
+    const CT* vn = (const CT*)a.v_new;
+
+    for (int idx = tid; idx < BQ * Dk; idx += ATT_THREADS) {
+        const int r = idx / Dk, d = idx - r * Dk;
+        Qs[r * Dkp + d] = r < nq ? a.q[((size_t)(i0 + r) * a.H + h) * Dk + d] : 0.f;
+    }
+    const int j_hi = p0 + i0 + nq - 1;
+    const int j_lo = a.window > 0 ? max(0, p0 + i0 - a.window + 1) : 0;
+
+    float m[4], l[4], O[4][DVT];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        if (a.sink_mode == CC_SINK_LEARNED) { m[r] = a.sink[h]; l[r] = 1.f; }
+        else if (a.sink_mode == CC_SINK_ZERO) { m[r] = 0.f; l[r] = 1.f; }
+        else { m[r] = -INFINITY; l[r] = 0.f; }
+#pragma unroll
+        for (int c = 0; c < DVT; ++c) O[r][c] = 0.f;
+    }
+
+    for (int jt = j_lo; jt <= j_hi; jt += BK) {
+        __syncthreads();  // the previous tile is consumed (first pass: nothing to wait for but harmless)
+        const int nk = min(BK, j_hi - jt + 1);
+        if (tid < BK) ksrc[tid] = tid < nk ? key_source(a, jt + tid, p0) : -1;
+        __syncthreads();
+        for (int idx = tid; idx < BK * Dk; idx += ATT_THREADS) {
+            const int r = idx / Dk, d = idx - r * Dk;
+            const int s = ksrc[r];
+            float v = 0.f;
+            if (s >= 0) v = ldf(kc, ((size_t)g * a.L + s) * Dk + d);
+            else if (s <= -2) v = ldf(kn, ((size_t)(-s - 2) * a.G + g) * Dk + d);
+            Ks[r * Dkp + d] = v;
+        }
+        for (int idx = tid; idx < BK * DVW; idx += ATT_THREADS) {
+            const int r = idx / DVW, c = idx - r * DVW;
+            const int s = ksrc[r];
+            float v = 0.f;
+            if (c < Dv) {
+                if (s >= 0) v = ldf(vc, ((size_t)g * a.L + s) * Dv + c);
+                else if (s <= -2) v = ldf(vn, ((size_t)(-s - 2) * a.G + g) * Dv + c);
+            }
+            Vs[r * DVW + c] = v;
+        }
+        __syncthreads();
+
+        float s[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[r][c] = 0.f;
+        for (int d = 0; d < Dk; ++d) {
+            float qv[4], kv[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) qv[r] = Qs[(ty * 4 + r) * Dkp + d];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) kv[c] = Ks[(tx + 16 * c) * Dkp + d];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) s[r][c] = fmaf(qv[r], kv[c], s[r][c]);
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int qi = ty * 4 + r;
+            const int i = p0 + i0 + qi;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int col = tx + 16 * c;
+                const int j = jt + col;
+                const bool ok = qi < nq && col < nk && ksrc[col] != -1 && j <= i && (a.window == 0 || i - j < a.window);
+                s[r][c] = ok ? s[r][c] * a.scale : -INFINITY;
+                mx = fmaxf(mx, s[r][c]);
+            }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float m_new = fmaxf(m[r], mx);
+            const float corr = (m[r] == -INFINITY) ? 0.f : expf(m[r] - m_new);
+            float rs = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float pr = (s[r][c] == -INFINITY) ? 0.f : expf(s[r][c] - m_new);
+                rs += pr;
+                Ss[qi * SP + tx + 16 * c] = pr;
+            }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o);
+            l[r] = l[r] * corr + rs;
+            m[r] = m_new;
+#pragma unroll
+            for (int c = 0; c < DVT; ++c) O[r][c] *= corr;
+        }
+        __syncwarp();
+        for (int k = 0; k < nk; ++k) {
+            float pv[4], vv[DVT];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) pv[r] = Ss[(ty * 4 + r) * SP + k];
+#pragma unroll
+            for (int c = 0; c < DVT; ++c) vv[c] = Vs[k * DVW + tx + 16 * c];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int c = 0; c < DVT; ++c) O[r][c] = fmaf(pv[r], vv[c], O[r][c]);
+        }
+    }
+    YT* y = (YT*)a.y;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int qi = ty * 4 + r;
+        if (qi >= nq) continue;
+        const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
+#pragma unroll
+        for (int c = 0; c < DVT; ++c) {
+            const int col = tx + 16 * c;
+            if (col < Dv) stf(y, ((size_t)(i0 + qi) * a.H + h) * Dv + col, O[r][c] * inv);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ decode attention
+constexpr int KS = 256;  // keys per CTA
+
+__host__ __device__ inline int decode_max_splits(int L, int window) {
+    const long long maxkeys = window > 0 ? (window < L + 1 ? window : L + 1) : (long long)L + 1;
+    return (int)((maxkeys + KS - 1) / KS);
+}
+
+template <typename CT>
+__device__ __forceinline__ void append_row(const CcSeqAttn& a, int g, int t, int p, int tid, int nthreads) {
+    const int slot = p % a.L;
+    CT* kc = (CT*)a.k_cache;
+    CT* vc = (CT*)a.v_cache;
+    const CT* kn = (const CT*)a.k_new;
+    const CT* vn = (const CT*)a.v_new;
+    for (int d = tid; d < a.Dk; d += nthreads) kc[((size_t)g * a.L + slot) * a.Dk + d] = kn[((size_t)t * a.G + g) * a.Dk + d];
+    for (int d = tid; d < a.Dv; d += nthreads) vc[((size_t)g * a.L + slot) * a.Dv + d] = vn[((size_t)t * a.G + g) * a.Dv + d];
+    if (tid == 0) {
+        if (a.mask != nullptr) a.mask[(size_t)g * a.L + slot] = 1;
+        if (g == 0) {
+            const int old = a.pos[slot];
+            a.pos[slot] = p;
+            if (old < 0 && a.cache_cts != nullptr) atomicAdd(a.cache_cts, 1);
+        }
+    }
+}
+
+template <typename CT, typename YT>
+__global__ void __launch_bounds__(KS) attn_decode_kernel(const CcSeqAttn a) {
+    extern __shared__ float sm[];
+    const int R = a.H / a.G, Dk = a.Dk, Dv = a.Dv;
+    float* qs = sm;             // [R, Dk]
+    float* S = qs + R * Dk;     // [R, KS]
+    int* ksrc = (int*)(S + R * KS);
+    __shared__ int s_last;
+
+    const int sp = blockIdx.x, g = blockIdx.y, tid = threadIdx.x;
+    const int p = a.input_pos[0];
+    const int j_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+    const int n = p - j_lo + 1;
+    const int nsplit = (n + KS - 1) / KS;
+    if (sp >= nsplit) return;
+    const int NS = decode_max_splits(a.L, a.window);
+    int* counters = (int*)a.workspace;
+    float* part_m = (float*)(counters + ((a.G + 3) & ~3));
+    float* part_l = part_m + (size_t)a.G * NS * R;
+    float* part_o = part_l + (size_t)a.G * NS * R;
+
+    const CT* kc = (const CT*)a.k_cache;
+    const CT* vc = (const CT*)a.v_cache;
+    const CT* kn = (const CT*)a.k_new;
+    const CT* vn = (const CT*)a.v_new;
+    for (int i = tid; i < R * Dk; i += KS) qs[i] = a.q[(size_t)g * R * Dk + i];
+    const int j = j_lo + sp * KS + tid;
+    int src = -1;
+    if (j <= p) src = key_source(a, j, p);
+    ksrc[tid] = src;
+    __syncthreads();
+    const int nk = min(KS, p - (j_lo + sp * KS) + 1);
+
+    if (src != -1) {
+        const CT* krow = src >= 0 ? kc + ((size_t)g * a.L + src) * Dk : kn + (size_t)g * Dk;
+        for (int r = 0; r < R; ++r) {
+            float acc = 0.f;
+            for (int d = 0; d < Dk; ++d) acc = fmaf(qs[r * Dk + d], ldf(krow, d), acc);
+            S[r * KS + tid] = acc * a.scale;
+        }
+    } else {
+        for (int r = 0; r < R; ++r) S[r * KS + tid] = -INFINITY;
+    }
+    __syncthreads();
+    const int warp = tid >> 5, lane = tid & 31;
+    const size_t pbase = ((size_t)g * NS + sp) * R;
+    for (int r = warp; r < R; r += KS / 32) {
+        float mx = -INFINITY;
+        for (int k = lane; k < KS; k += 32) mx = fmaxf(mx, S[r * KS + k]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int k = lane; k < KS; k += 32) {
+            const float sv = S[r * KS + k];
+            const float pr = sv == -INFINITY ? 0.f : expf(sv - mx);
+            S[r * KS + k] = pr;
+            sum += pr;
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) { part_m[pbase + r] = mx; part_l[pbase + r] = sum; }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < R * Dv; idx += KS) {
+        const int r = idx / Dv, c = idx - r * Dv;
+        float acc = 0.f;
+        for (int k = 0; k < nk; ++k) {
+            const int s = ksrc[k];
+            if (s == -1) continue;
+            const float v = s >= 0 ? ldf(vc, ((size_t)g * a.L + s) * Dv + c) : ldf(vn, (size_t)g * Dv + c);
+            acc = fmaf(S[r * KS + k], v, acc);
+        }
+        part_o[(pbase + r) * Dv + c] = acc;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(&counters[g], 1) == nsplit - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // the last CTA of this head: every other CTA of the head has finished reading; combine in split order
+    YT* y = (YT*)a.y;
+    const volatile float* vm = part_m;
+    const volatile float* vl = part_l;
+    const volatile float* vo = part_o;
+    for (int idx = tid; idx < R * Dv; idx += KS) {
+        const int r = idx / Dv, c = idx - r * Dv;
+        const int h = g * R + r;
+        float M = -INFINITY, Lsum = 0.f;
+        if (a.sink_mode == CC_SINK_LEARNED) M = a.sink[h];
+        else if (a.sink_mode == CC_SINK_ZERO) M = 0.f;
+        const float sinkv = M;
+        for (int s = 0; s < nsplit; ++s) M = fmaxf(M, vm[((size_t)g * NS + s) * R + r]);
+        if (a.sink_mode != CC_SINK_NONE) Lsum = expf(sinkv - M);
+        float acc = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            const size_t b = ((size_t)g * NS + s) * R + r;
+            const float ms = vm[b];
+            const float w = ms == -INFINITY ? 0.f : expf(ms - M);
+            Lsum += vl[b] * w;
+            acc += vo[b * Dv + c] * w;
+        }
+        stf(y, (size_t)h * Dv + c, Lsum > 0.f ? acc / Lsum : 0.f);
+    }
+    if (tid == 0) counters[g] = 0;
+    if (a.append) append_row<CT>(a, g, 0, p, tid, KS);
+}
+
+template <typename CT>
+__global__ void cache_append_kernel(const CcSeqAttn a, int t_first) {
+    const int t = t_first + blockIdx.x, g = blockIdx.y;
+    append_row<CT>(a, g, t, a.input_pos[0] + t, threadIdx.x, blockDim.x);
+}
+
+// ------------------------------------------------------------------------------------------------ post-sum norm
+template <typename YT, typename AT>
+__global__ void residual_norm_kernel(float* __restrict__ x, const YT* __restrict__ y, const float* __restrict__ w,
+                                     float alpha, float eps, AT* __restrict__ x_act, int E) {
+    __shared__ float red[32];
+    const size_t base = (size_t)blockIdx.x * E;
+    float ss = 0.f;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        float s = alpha * x[base + e];
+        if (y != nullptr) s += ldf(y, base + e);
+        ss += s * s;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+        v = warp_sum(v);
+        if (threadIdx.x == 0) red[0] = v;
+    }
+    __syncthreads();
+    const float r = 1.0f / sqrtf(red[0] / (float)E + eps);
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        float s = alpha * x[base + e];
+        if (y != nullptr) s += ldf(y, base + e);
+        const float v = s * r * (1.0f + w[e]);
+        x[base + e] = v;
+        if (x_act != nullptr) stf(x_act, base + e, v);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ clamped gated unit
+template <typename IT, typename OT>
+__global__ void clamped_glu_kernel(const IT* __restrict__ gu, OT* __restrict__ out, float limit, float slope, int T,
+                                   int F) {
+    const size_t n = (size_t)T * F;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / F, f = i - t * F;
+        const float g = fminf(ldf(gu, t * 2 * F + f), limit);
+        const float u = fminf(fmaxf(ldf(gu, t * 2 * F + F + f), -limit), limit);
+        stf(out, i, g * (1.0f / (1.0f + expf(-slope * g))) * (u + 1.0f));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+static int check_attn(const CcSeqAttn* a) {
+    if (!a || !a->q || !a->k_new || !a->v_new || !a->k_cache || !a->v_cache || !a->pos || !a->input_pos || !a->y)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "attention: NULL pointer");
+    if (a->T < 1 || a->H < 1 || a->G < 1 || a->H % a->G || a->Dk < 1 || a->Dv < 1 || a->L < 1 || a->window < 0)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "attention: bad sizes");
+    if (a->Dk > 256 || a->Dv > 256) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "attention: head sizes above 256");
+    if (a->window > 0 && a->L < a->window)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "attention: cache capacity below the window");
+    if (a->sink_mode == CC_SINK_LEARNED && !a->sink) return fail(CC_SEQ_ERR_INVALID_ARG, "attention: sink missing");
+    return CC_SEQ_OK;
+}
+
+template <typename CT, typename YT, int DVT>
+static int launch_chunk(const CcSeqAttn* a, cudaStream_t st) {
+    const int Dkp = a->Dk | 1;
+    const size_t smem = sizeof(float) * ((size_t)BQ * Dkp + (size_t)BK * Dkp + (size_t)BK * 16 * DVT + (size_t)BQ * (BK + 1)) + sizeof(int) * BK;
+    auto kern = attn_chunk_kernel<CT, YT, DVT>;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        configured = smem;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(CC_SEQ_ERR_CUDA, cudaGetErrorString(e));
+    }
+    dim3 grid((a->T + BQ - 1) / BQ, a->H);
+    kern<<<grid, ATT_THREADS, smem, st>>>(*a);
+    return cuda_check("attn_chunk_kernel");
+}
+
+template <typename CT, typename YT>
+static int dispatch_chunk(const CcSeqAttn* a, cudaStream_t st) {
+    const int need = (a->Dv + 15) / 16;
+    if (need <= 1) return launch_chunk<CT, YT, 1>(a, st);
+    if (need <= 2) return launch_chunk<CT, YT, 2>(a, st);
+    if (need <= 3) return launch_chunk<CT, YT, 3>(a, st);
+    if (need <= 4) return launch_chunk<CT, YT, 4>(a, st);
+    if (need <= 6) return launch_chunk<CT, YT, 6>(a, st);
+    if (need <= 8) return launch_chunk<CT, YT, 8>(a, st);
+    return launch_chunk<CT, YT, 16>(a, st);
+}
+
+template <typename CT, typename YT>
+static int launch_decode(const CcSeqAttn* a, cudaStream_t st) {
+    const int R = a->H / a->G;
+    const size_t smem = sizeof(float) * ((size_t)R * a->Dk + (size_t)R * KS) + sizeof(int) * KS;
+    auto kern = attn_decode_kernel<CT, YT>;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        configured = smem;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(CC_SEQ_ERR_CUDA, cudaGetErrorString(e));
+    }
+    dim3 grid(decode_max_splits(a->L, a->window), a->G);
+    kern<<<grid, KS, smem, st>>>(*a);
+    return cuda_check("attn_decode_kernel");
+}
+
+#define CCS_DISPATCH2(d0, d1, CALL)                                                              \
+    do {                                                                                         \
+        if ((d0) == CC_DT_F32 && (d1) == CC_DT_F32) return CALL(float, float);                   \
+        if ((d0) == CC_DT_F32 && (d1) == CC_DT_BF16) return CALL(float, __nv_bfloat16);          \
+        if ((d0) == CC_DT_BF16 && (d1) == CC_DT_F32) return CALL(__nv_bfloat16, float);          \
+        if ((d0) == CC_DT_BF16 && (d1) == CC_DT_BF16) return CALL(__nv_bfloat16, __nv_bfloat16); \
+        return fail(CC_SEQ_ERR_INVALID_ARG, "unknown element type");                             \
+    } while (0)
+
+}  // namespace ccs
+
+using namespace ccs;
+
+extern "C" {
+
+int cc_seq_abi_version(void) { return CC_SEQ_ABI_VERSION; }
+const char* cc_seq_last_error(void) { return g_err; }
+
+int cc_seq_embed(const int32_t* tokens, const int32_t* input_pos, int32_t* prev_token, const void* embed,
+                 const void* bigram, const float* inv_freq, float* x, void* x_act, int32_t T, int32_t E, float scale,
+                 int32_t buckets, int32_t mul_prev, int32_t mul_cur, int32_t table_dtype, int32_t act_dtype, void* stream) {
+    if (!tokens || !input_pos || !prev_token || !embed || !inv_freq || !x || T < 1 || E < 1 || (bigram && buckets < 1))
+        return fail(CC_SEQ_ERR_INVALID_ARG, "embed: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(WT, AT)                                                                                                  \
+    (embed_kernel<WT, AT><<<T, 128, 0, st>>>(tokens, input_pos, prev_token, (const WT*)embed, (const WT*)bigram,      \
+                                             inv_freq, x, (AT*)x_act, T, E, scale, buckets, mul_prev, mul_cur),       \
+     cuda_check("embed_kernel"))
+    CCS_DISPATCH2(table_dtype, act_dtype, CALL);
+#undef CALL
+}
+
+int cc_seq_qkv_prepare(const void* qkv, int32_t in_dtype, const float* bias, const int32_t* input_pos,
+                       const float* mix_lambda, const void* v_first, float* q_out, void* k_out, void* v_out,
+                       int32_t out_dtype, int32_t T, int32_t H, int32_t G, int32_t Dk, int32_t Dv, float eps,
+                       int32_t unit_norm, float gain_coef, int32_t gain_every, void* stream) {
+    if (!qkv || !input_pos || !q_out || !k_out || !v_out || T < 1 || H < 1 || G < 1 || Dk < 1 || Dv < 1 ||
+        (v_first && !mix_lambda))
+        return fail(CC_SEQ_ERR_INVALID_ARG, "qkv_prepare: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(IT, OT)                                                                                                   \
+    (qkv_prepare_kernel<IT, OT><<<T, 128, 0, st>>>((const IT*)qkv, bias, input_pos, mix_lambda, (const OT*)v_first,    \
+                                                   q_out, (OT*)k_out, (OT*)v_out, T, H, G, Dk, Dv, eps, unit_norm,     \
+                                                   gain_coef, gain_every),                                             \
+     cuda_check("qkv_prepare_kernel"))
+    CCS_DISPATCH2(in_dtype, out_dtype, CALL);
+#undef CALL
+}
+
+int cc_seq_attention(const CcSeqAttn* a, void* stream) {
+    int rc = check_attn(a);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(CT, YT) dispatch_chunk<CT, YT>(a, st)
+    CCS_DISPATCH2(a->cache_dtype, a->y_dtype, CALL);
+#undef CALL
+}
+
+uint64_t cc_seq_decode_workspace(int32_t H, int32_t G, int32_t Dv, int32_t L, int32_t window) {
+    const uint64_t NS = (uint64_t)decode_max_splits(L, window);
+    return sizeof(int) * (uint64_t)((G + 3) & ~3) + sizeof(float) * NS * (uint64_t)H * (2 + (uint64_t)Dv);
+}
+
+int cc_seq_attention_decode(const CcSeqAttn* a, void* stream) {
+    int rc = check_attn(a);
+    if (rc) return rc;
+    if (a->T != 1) return fail(CC_SEQ_ERR_INVALID_ARG, "attention_decode: one token per call");
+    if (!a->workspace || a->workspace_bytes < cc_seq_decode_workspace(a->H, a->G, a->Dv, a->L, a->window))
+        return fail(CC_SEQ_ERR_INVALID_ARG, "attention_decode: workspace missing or too small");
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(CT, YT) launch_decode<CT, YT>(a, st)
+    CCS_DISPATCH2(a->cache_dtype, a->y_dtype, CALL);
+#undef CALL
+}
+
+int cc_seq_cache_append(const CcSeqAttn* a, void* stream) {
+    if (!a || !a->k_new || !a->v_new || !a->k_cache || !a->v_cache || !a->pos || !a->input_pos || a->T < 1 || a->L < 1)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "cache_append: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int t_first = a->T > a->L ? a->T - a->L : 0;
+    dim3 grid(a->T - t_first, a->G);
+    if (a->cache_dtype == CC_DT_F32) cache_append_kernel<float><<<grid, 64, 0, st>>>(*a, t_first);
+    else if (a->cache_dtype == CC_DT_BF16) cache_append_kernel<__nv_bfloat16><<<grid, 64, 0, st>>>(*a, t_first);
+    else return fail(CC_SEQ_ERR_INVALID_ARG, "cache_append: unknown element type");
+    return cuda_check("cache_append_kernel");
+}
+
+int cc_seq_residual_norm(float* x, const void* y, int32_t y_dtype, const float* w, float alpha, float eps, void* x_act,
+                         int32_t act_dtype, int32_t T, int32_t E, void* stream) {
+    if (!x || !w || T < 1 || E < 1) return fail(CC_SEQ_ERR_INVALID_ARG, "residual_norm: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(YT, AT)                                                                                                \
+    (residual_norm_kernel<YT, AT><<<T, 256, 0, st>>>(x, (const YT*)y, w, alpha, eps, (AT*)x_act, E),                \
+     cuda_check("residual_norm_kernel"))
+    CCS_DISPATCH2(y_dtype, act_dtype, CALL);
+#undef CALL
+}
+
+int cc_seq_clamped_glu(const void* gu, void* out, int32_t io_dtype, int32_t out_dtype, float limit, float slope,
+                       int32_t T, int32_t F, void* stream) {
+    if (!gu || !out || T < 1 || F < 1) return fail(CC_SEQ_ERR_INVALID_ARG, "clamped_glu: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t n = (size_t)T * F;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+#define CALL(IT, OT)                                                                                    \
+    (clamped_glu_kernel<IT, OT><<<blocks, 256, 0, st>>>((const IT*)gu, (OT*)out, limit, slope, T, F),   \
+     cuda_check("clamped_glu_kernel"))
+    CCS_DISPATCH2(io_dtype, out_dtype, CALL);
+#undef CALL
+}
+
+}  // extern "C"

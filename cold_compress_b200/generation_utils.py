@@ -50,6 +50,8 @@ def add_generation_arguments(parser: argparse.ArgumentParser):
                        help="Capture the decode step in a CUDA graph (the reference's torch.compile switch).")
     group.add_argument("--device", type=str, default=default_device, help="Device to use")
     group.add_argument("--attn_top_k", type=float, default=1.0, help="Kept for CLI compatibility; must be 1.0.")
+    group.add_argument("--prefill_chunk", type=int, default=None,
+                       help="Feed the prompt in portions of this many tokens (models that continue a prompt from their caches).")
 
 
 def merge_cache_config(args):
@@ -93,12 +95,22 @@ def greedy(logits, next_token):
     return next_token, probs
 
 
+def model_step(model, x: torch.Tensor, input_pos: torch.Tensor, is_prefill: bool, attn_top_k: float = 1,
+               logits_at: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The one forward step behind prefill, decode and trace replay: tokens x [1, T] at positions input_pos through the
+    model and its caches; logits [1, n, vocab].  `logits_at` (rows of this step whose logits are wanted) is for models
+    that serve it; the default is the last row.  No S x S bool mask is built: causality is applied inside the
+    attention (the reference builds the mask on the host, generation_utils.py:153-158)."""
+    if logits_at is not None:
+        return model(x, input_pos, is_prefill=is_prefill, logits_at=logits_at)
+    if is_prefill:
+        return model(x, input_pos, mask=None, is_prefill=True)
+    return model(x, input_pos, is_prefill=False, attn_top_k=attn_top_k)
+
+
 def prefill(model: Transformer, x: torch.Tensor, input_pos: torch.Tensor, next_token: torch.Tensor = None,
             **sampling_kwargs):
-    # no S x S bool mask: causality is applied inside the attention (the reference builds the
-    # mask on the host, generation_utils.py:153-158)
-    logits = model(x, input_pos, mask=None, is_prefill=True)
-    return greedy(logits, next_token)
+    return greedy(model_step(model, x, input_pos, True), next_token)
 
 
 def decode_one_token(model: Transformer, x: torch.Tensor, input_pos: torch.Tensor, next_token: torch.Tensor = None,
@@ -107,8 +119,7 @@ def decode_one_token(model: Transformer, x: torch.Tensor, input_pos: torch.Tenso
     if fused is not None:   # ONE kernel: the whole layer stack, the head, arg-max and softmax (csrc/decode_token.cu)
         tok, probs = fused
         return (tok if next_token is None else next_token), probs
-    logits = model(x, input_pos, is_prefill=False, attn_top_k=attn_top_k)
-    return greedy(logits, next_token=next_token)
+    return greedy(model_step(model, x, input_pos, False, attn_top_k=attn_top_k), next_token=next_token)
 
 
 class GraphedDecoder:
@@ -228,6 +239,11 @@ def apply_pattern(pattern: list, out_size: int, extension_strategy: str = "tile"
 def setup_caches(model: Transformer, tokenizer, device, max_seq_length: int, cache_kwargs: dict = None) -> dict:
     """Expand the CLI-level cache kwargs to per-layer values and build the caches
     (reference generation_utils.py:324-388)."""
+    if hasattr(model, "layer_cache_plan"):   # the layer types fix the cache kinds (full / window ring) themselves
+        ck = model.layer_cache_plan(cache_kwargs, max_seq_length)
+        with torch.device(device):
+            model.setup_caches(max_batch_size=1, **ck)
+        return ck
     ck = cache_kwargs
     n_layer = model.config.n_layer
     ck["max_seq_length"] = max_seq_length
@@ -263,7 +279,7 @@ def get_cache_stats(model: Transformer, prompt_len: int, gen_len: int):
 def generate(model: Transformer, prompt: torch.Tensor, prefill: callable, decode_one_token: callable,
              max_new_tokens: int, next_tokens: Optional[torch.Tensor] = None, terminator_ids: Optional[list] = None,
              feed_long_prompts: bool = False, decode_first_token: bool = False, attn_top_k: float = 1,
-             **sampling_kwargs):
+             prefill_chunk: Optional[int] = None, **sampling_kwargs):
     """Prefill the prompt, then decode; returns (sequence, per-token probabilities, perf stats)
     with the reference's accounting (generation_utils.py:399-531)."""
     prompt_length = prompt.size(0)
@@ -293,7 +309,15 @@ def generate(model: Transformer, prompt: torch.Tensor, prefill: callable, decode
 
     device_sync(device)
     t0 = time.perf_counter()
-    tok, tok_probs = prefill(model, prompt.view(1, -1), input_pos, next_token=next_token, **sampling_kwargs)
+    if prefill_chunk and prefill_chunk < prompt_length:
+        # the prompt in portions: each step continues from the caches the previous one left; the last one samples
+        assert getattr(model, "supports_prompt_portions", False), "this model prefills its prompt in one step"
+        for lo in range(0, prompt_length, prefill_chunk):
+            hi = min(prompt_length, lo + prefill_chunk)
+            tok, tok_probs = prefill(model, prompt[lo:hi].view(1, -1), input_pos[lo:hi], next_token=next_token,
+                                     **sampling_kwargs)
+    else:
+        tok, tok_probs = prefill(model, prompt.view(1, -1), input_pos, next_token=next_token, **sampling_kwargs)
     device_sync(device)
     t1 = time.perf_counter()
     tok, tok_probs = tok.clone(), tok_probs.clone()
@@ -324,6 +348,15 @@ def generate(model: Transformer, prompt: torch.Tensor, prefill: callable, decode
 # --------------------------------------------------------------------------- model loading
 
 def load_model(checkpoint_path, device, precision, use_tp):
+    """A gpt-fast `model.pth` whose folder name selects the Llama-family shape (reference generation_utils.py:534-566),
+    or a folder with config.json + model.safetensors whose `architecture` selects a registered model class."""
+    from .checkpoint import is_checkpoint_folder, load_checkpoint_folder
+    folder = checkpoint_path if is_checkpoint_folder(checkpoint_path) else (
+        checkpoint_path.parent if Path(checkpoint_path).name == "model.safetensors" else None)
+    if folder is not None:
+        if use_tp:
+            raise NotImplementedError("tensor parallelism is wired for the Llama-family model only")
+        return load_checkpoint_folder(folder, device, precision)
     with torch.device("meta"):
         model = Transformer.from_name(checkpoint_path.parent.name)
     if "int8" in str(checkpoint_path) or "int4" in str(checkpoint_path):
