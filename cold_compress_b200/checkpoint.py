@@ -79,3 +79,22 @@ def load_checkpoint_folder(path, device, precision=torch.bfloat16):
     if unused:
         print(f"note: {len(unused)} checkpoint tensors are not used by {arch}: {unused[:8]}")
     return model.to(device).eval()
+
+
+def write_safetensors(path, tensors: Dict[str, torch.Tensor]):
+    """The inverse of read_safetensors (used to export random-init checkpoints for benchmarks and tests)."""
+    names = {v: k for k, v in _DTYPES.items()}
+    header, blobs, off = {}, [], 0
+    for name in sorted(tensors):
+        t = tensors[name].detach().cpu().contiguous()
+        raw = t.view(torch.uint8).numpy().tobytes() if t.dim() else t.reshape(1).view(torch.uint8).numpy().tobytes()
+        header[name] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    head = json.dumps(header, separators=(",", ":")).encode("utf-8")
+    head += b" " * (-len(head) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(head)))
+        f.write(head)
+        for b in blobs:
+            f.write(b)
