@@ -656,6 +656,168 @@ def run_reference(args):
     print(json.dumps(out), flush=True)
 
 
+# --------------------------------------------------------------------------- model-design comparison (--design)
+
+DESIGN_SIZES = {
+    # name: width, query heads, kv heads, head size, feed-forward, layers, vocab, prompt, window of the sliding layers
+    "1b": dict(width=2048, heads=16, kv_heads=4, head=128, ff=8192, layers=4, vocab=32000, prompt=4096, window=1024),
+    "8b": dict(width=4096, heads=32, kv_heads=8, head=128, ff=14336, layers=4, vocab=32000, prompt=4096, window=1024),
+    "8b-long": dict(width=4096, heads=32, kv_heads=8, head=128, ff=14336, layers=2, vocab=32000, prompt=16384, window=4096),
+}
+
+
+def _tidelorn_model(sz, device, dtype):
+    """A random-init Tidelorn of the given layer shape: global and sliding layers alternate, all with value mixing."""
+    from cold_compress_b200.tidelorn import TidelornTransformer
+    mixer = dict(heads=sz["heads"], kv_heads=sz["kv_heads"], dim=sz["head"], vdim=sz["head"], scale=sz["head"] ** -0.5, v_mix=True)
+    layers = []
+    for i in range(sz["layers"]):
+        kind = "attention" if i % 2 == 0 else "attention_2"
+        extra = {"q_temp": {"coef": 0.3, "every": 256}} if kind == "attention" else {"mask": {"size": sz["window"]}}
+        layers.append({"type": kind, "mixer": dict(mixer, **extra), "mlp": {"kind": "dense", "ff": sz["ff"], "limit": 7.0}})
+    cfg = {"architecture": "Tidelorn", "vocab": sz["vocab"], "width": sz["width"], "postln_alpha": 2.0, "norm": {"eps": 1e-6},
+           "embedding": {"scale": sz["width"] ** 0.5, "bigram": {"buckets": 100003, "mul_prev": 31, "mul_cur": 7}}, "layers": layers}
+    with torch.device(device):
+        model = TidelornTransformer.from_config(cfg, dtype)
+    gen = torch.Generator(device=device).manual_seed(0)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.empty(p.shape, device=device).normal_(0.0, 0.02, generator=gen))
+            elif "vmix" in name:
+                p.fill_(0.5)
+    return model.eval()
+
+
+def _llama_model(sz, device):
+    from cold_compress_b200.model import ModelArgs, Transformer
+    cfg = ModelArgs(block_size=sz["prompt"] + 1024, vocab_size=sz["vocab"], n_layer=sz["layers"], n_head=sz["heads"],
+                    n_local_heads=sz["kv_heads"], dim=sz["width"], intermediate_size=sz["ff"], max_length=sz["prompt"] + 1024)
+    with torch.device(device):
+        model = Transformer(cfg).to(torch.bfloat16)
+    gen = torch.Generator(device=device).manual_seed(0)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            p.fill_(1.0) if "norm" in name else p.normal_(0.0, 0.02, generator=gen)
+    return model.eval()
+
+
+def _time_events(fn, warmup, steps, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(steps):
+        if flush is not None:
+            flush.add_(1)      # a write larger than L2 between timed iterations
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    return total / steps
+
+
+def run_design(args):
+    """`--design`: prefill and decode throughput of the Tidelorn design beside the Llama-family model with a full
+    cache at the same layer shape (random weights, synthetic tokens, one GPU), plus the design's attention kernels
+    alone against their rooflines.  Prefill = one step over the prompt; decode = graph-captured single-token steps at
+    that context.  Timed with CUDA events after warm-up; a 256 MiB buffer is rewritten between timed prefill steps."""
+    from cold_compress_b200 import generation_utils as gu
+    from cold_compress_b200.tokenizer import SyntheticTokenizer
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    hbm, _ = peaks()
+    names = [n for n in args.design.split(",") if n]
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=device)
+    rows = []
+    for name in names:
+        sz = DESIGN_SIZES[name]
+        P = sz["prompt"]
+        prompt = torch.randint(0, sz["vocab"], (P,), dtype=torch.int32, device=device, generator=torch.Generator(device=device).manual_seed(1))
+        row = {"size": name, **sz}
+        for arm in ("tidelorn", "llama"):
+            model = _tidelorn_model(sz, device, torch.bfloat16) if arm == "tidelorn" else _llama_model(sz, device)
+            ck = cache_kwargs(dict(slots=1.0, pattern="tile", strategy="full", compressor="recent_global"))
+            ck["global_tokens"] = 0
+            gu.setup_caches(model, SyntheticTokenizer(vocab_size=sz["vocab"]), device, P + 1024, ck)
+            pos = torch.arange(P, device=device)
+
+            def prefill_once():
+                gu.reset_caches(model)
+                return gu.prefill(model, prompt.view(1, -1), pos)
+
+            with torch.no_grad():
+                ms = _time_events(prefill_once, 2, 3, flush)
+                tok, _ = prefill_once()
+                decoder = gu.GraphedDecoder()
+                input_pos = torch.tensor([P], dtype=torch.int32, device=device)
+                cur = [tok.view(1, 1).clone()]
+
+                def decode_once():
+                    nxt, _ = decoder(model, cur[0], input_pos)
+                    input_pos.add_(1)
+                    cur[0] = nxt.view(1, 1)
+
+                for _ in range(4):
+                    decode_once()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(args.steps):
+                    decode_once()
+                b.record()
+                torch.cuda.synchronize()
+                dms = a.elapsed_time(b) / args.steps
+            wbytes = sum(p.numel() * p.element_size() for n, p in model.named_parameters() if p.dim() >= 2 and "tok_embeddings" not in n and "bigram" not in n)
+            row[arm] = {"prefill_tokens_per_s": round(P / ms * 1e3, 1), "prefill_ms": round(ms, 3),
+                        "decode_tokens_per_s": round(1e3 / dms, 1), "decode_ms": round(dms, 4),
+                        "decode_weight_stream_frac_of_hbm": round(wbytes / (dms * 1e-3) / 1e9 / hbm, 3),
+                        "kernels_per_token": model.kernels_per_token()}
+            del model, decoder
+            torch.cuda.empty_cache()
+        row["kernels"] = _design_kernels(sz, device, hbm)
+        rows.append(row)
+    print(json.dumps({"metric": "prefill and decode tokens/s, Tidelorn beside Llama (full cache) at equal layer shape",
+                      "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "steps": args.steps, "sizes": rows,
+                      "peaks": {"hbm_gbs": hbm}}), flush=True)
+
+
+def _design_kernels(sz, device, hbm):
+    """The design's attention kernels alone at this shape: the chunk kernel over a whole prompt (fp32 FMA work:
+    4 * S^2/2 * D per query head for the global layer) and the one-token kernel at that context (bytes of the live rows)."""
+    from cold_compress_b200 import seq_ops
+    from cold_compress_b200.cache import get_cache_constructor
+    H, G, D, P = sz["heads"], sz["kv_heads"], sz["head"], sz["prompt"]
+    out = {}
+    gen = torch.Generator(device=device).manual_seed(2)
+    q = torch.randn(P, H, D, device=device, generator=gen)
+    k = torch.randn(P, G, D, device=device, generator=gen).to(torch.bfloat16)
+    v = torch.randn(P, G, D, device=device, generator=gen).to(torch.bfloat16)
+    y = torch.empty(P, H, D, device=device, dtype=torch.bfloat16)
+    ip0 = torch.zeros(1, dtype=torch.int32, device=device)
+    for label, window, strategy, L in (("global", 0, "full", P + 8), ("window", sz["window"], "recent_global", sz["window"])):
+        ctor, _ = get_cache_constructor(strategy)
+        with torch.device(device):
+            cache = ctor(1, G, D, torch.bfloat16, max_cache_length=L, global_tokens=0, max_seq_length=P + 8, cache_bits=None)
+        args = (q, k, v, cache.k_cache, cache.v_cache, cache.pos, cache.mask, cache.cache_cts, ip0, y, None, window, 2, D ** -0.5)
+        ms = _time_events(lambda: seq_ops.seq_attention(*args, seq_ops.ATTN_CHUNK, None), 2, 3)
+        pairs = P * (P + 1) / 2 if not window else sum(min(i + 1, window) for i in range(P))
+        out[f"prefill_attention_{label}"] = {"ms": round(ms, 3), "fp32_tflops": round(4 * pairs * D * H / ms / 1e9, 2)}
+        seq_ops.seq_attention(*args, seq_ops.ATTN_APPEND_ONLY, None)
+        ipd = torch.tensor([P], dtype=torch.int32, device=device)
+        ws = cache._sequence_workspace(H, window)
+        dargs = (q[:1], k[:1], v[:1], cache.k_cache, cache.v_cache, cache.pos, cache.mask, cache.cache_cts, ipd, y[:1], None, window, 2, D ** -0.5)
+        us = _time_events(lambda: seq_ops.seq_attention(*dargs, seq_ops.ATTN_DECODE, ws), 5, 20) * 1e3
+        live = min(P, window) if window else P
+        nbytes = 2 * G * live * D * 2
+        out[f"decode_attention_{label}"] = {"us": round(us, 2), "gb_per_s": round(nbytes / us / 1e3, 1),
+                                            "frac_of_hbm": round(nbytes / us / 1e3 / hbm, 3)}
+    return out
+
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -665,7 +827,12 @@ def main():
     ap.add_argument("--config", type=int, default=0, choices=[0, 1, 2, 3, 4, 5],
                     help="BASELINE.json config (default: 2 on one GPU, 5 = pyramid lengths under head sharding on several)")
     ap.add_argument("--k1", action="store_true", help="also time the per-layer decode kernel (cc_decode_step) alone")
+    ap.add_argument("--design", default="", metavar="SIZES",
+                    help="instead of the headline workload: Tidelorn beside the Llama-family model at equal layer shape, "
+                         "comma-separated sizes of " + "/".join(DESIGN_SIZES))
     args = ap.parse_args()
+    if args.design:
+        return run_design(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -120,7 +120,7 @@ __global__ void qkv_prepare_kernel(const IT* __restrict__ qkv, const float* __re
 }
 
 // ------------------------------------------------------------------------------------------------ chunk attention
-constexpr int BQ = 64, BK = 64, ATT_THREADS = 256;
+constexpr int BQ = 64, BK = 32, ATT_THREADS = 256;
 
 __device__ __forceinline__ int key_source(const CcSeqAttn& a, int j, int p0) {
     // >= 0: cache slot, -1: not a key, <= -2: row -(s + 2) of the chunk
@@ -129,11 +129,64 @@ __device__ __forceinline__ int key_source(const CcSeqAttn& a, int j, int p0) {
     return a.pos[slot] == j ? slot : -1;
 }
 
-template <typename CT, typename YT, int DVT>
+// Stages `rows` rows of `width` elements (global, row r at src(r), or zeros when src(r) == nullptr) into fp32 shared
+// memory rows of `stride` floats.  16-byte loads when the rows allow it, element loads otherwise.
+template <typename CT, typename SrcFn>
+__device__ __forceinline__ void stage_rows(float* dst, int stride, int rows, int width, SrcFn src, int tid, int nthreads) {
+    constexpr int VEC = 16 / (int)sizeof(CT);
+    if (width % VEC == 0) {
+        constexpr int U = 4;   // loads in flight per thread
+        const int per_row = width / VEC, total = rows * per_row;
+        for (int base = tid; base < total; base += nthreads * U) {
+            uint4 u[U];
+            int off[U];
+#pragma unroll
+            for (int e = 0; e < U; ++e) {
+                const int idx = base + e * nthreads;
+                off[e] = -1;
+                u[e] = make_uint4(0u, 0u, 0u, 0u);
+                if (idx < total) {
+                    const int r = idx / per_row, c = (idx - r * per_row) * VEC;
+                    off[e] = r * stride + c;
+                    const CT* p = src(r);
+                    if (p != nullptr) u[e] = __ldg(reinterpret_cast<const uint4*>(p + c));
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < U; ++e) {
+                if (off[e] < 0) continue;
+                const CT* e8 = reinterpret_cast<const CT*>(&u[e]);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) dst[off[e] + i] = ldf(e8, i);
+            }
+        }
+    } else {
+        for (int idx = tid; idx < rows * width; idx += nthreads) {
+            const int r = idx / width, c = idx - r * width;
+            const CT* p = src(r);
+            dst[r * stride + c] = p == nullptr ? 0.f : ldf(p, c);
+        }
+    }
+}
+
+
+// Row stride (floats) of a shared-memory tile read with 16-byte loads by lanes that hold different rows: a multiple
+// of 4 whose quarter is odd, so that eight rows fall into eight different 16-byte bank groups.
+__host__ __device__ inline int vec_stride(int width) {
+    const int w4 = (width + 3) / 4;
+    return 4 * (w4 | 1);
+}
+
+// CTA = 64 consecutive queries of one query head; key tiles of 32 positions.  Thread (ty, tx) of the 16 x 16 grid owns
+// score rows 4 ty .. 4 ty + 3 x columns tx, tx + 16 and output rows 4 ty .. x value columns 64 c + 4 tx .. 4 tx + 3.
+// All shared-memory operands are read with 16-byte loads: q, k along the head dimension, P along the keys, V along
+// the value columns; 32 (scores) and 64 DV4 (values) FMAs per 6 and 4 + 4 DV4 loads.
+template <typename CT, typename YT, int DV4>
 __global__ void __launch_bounds__(ATT_THREADS) attn_chunk_kernel(const CcSeqAttn a) {
-    extern __shared__ float sm[];
-    const int Dk = a.Dk, Dv = a.Dv, Dkp = Dk | 1;
-    constexpr int DVW = 16 * DVT, SP = BK + 1;
+    extern __shared__ float4 sm4[];
+    float* sm = reinterpret_cast<float*>(sm4);
+    const int Dk = a.Dk, Dv = a.Dv, Dkp = vec_stride(Dk), Dk4 = (Dk + 3) / 4;
+    constexpr int DVW = 64 * DV4, SP = BK + 4;
     float* Qs = sm;
     float* Ks = Qs + BQ * Dkp;
     float* Vs = Ks + BK * Dkp;
@@ -150,63 +203,68 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_chunk_kernel(const CcSeqAttn
     const CT* kn = (const CT*)a.k_new;
     const CT* vn = (const CT*)a.v_new;
 
-    for (int idx = tid; idx < BQ * Dk; idx += ATT_THREADS) {
-        const int r = idx / Dk, d = idx - r * Dk;
-        Qs[r * Dkp + d] = r < nq ? a.q[((size_t)(i0 + r) * a.H + h) * Dk + d] : 0.f;
+    // padding columns are zero for the whole kernel (the tile loads below never touch them)
+    for (int idx = tid; idx < (BQ + BK) * (Dkp - Dk); idx += ATT_THREADS) {
+        const int r = idx / (Dkp - Dk), c = Dk + idx - r * (Dkp - Dk);
+        Qs[r * Dkp + c] = 0.f;   // Ks follows Qs with the same stride
     }
+    for (int idx = tid; idx < BK * (DVW - Dv); idx += ATT_THREADS) {
+        const int r = idx / (DVW - Dv), c = Dv + idx - r * (DVW - Dv);
+        Vs[r * DVW + c] = 0.f;
+    }
+    stage_rows<float>(Qs, Dkp, BQ, Dk, [&](int r) -> const float* {
+        return r < nq ? a.q + ((size_t)(i0 + r) * a.H + h) * Dk : nullptr;
+    }, tid, ATT_THREADS);
     const int j_hi = p0 + i0 + nq - 1;
     const int j_lo = a.window > 0 ? max(0, p0 + i0 - a.window + 1) : 0;
 
-    float m[4], l[4], O[4][DVT];
+    float m[4], l[4], O[4][4 * DV4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
         if (a.sink_mode == CC_SINK_LEARNED) { m[r] = a.sink[h]; l[r] = 1.f; }
         else if (a.sink_mode == CC_SINK_ZERO) { m[r] = 0.f; l[r] = 1.f; }
         else { m[r] = -INFINITY; l[r] = 0.f; }
 #pragma unroll
-        for (int c = 0; c < DVT; ++c) O[r][c] = 0.f;
+        for (int c = 0; c < 4 * DV4; ++c) O[r][c] = 0.f;
     }
 
     for (int jt = j_lo; jt <= j_hi; jt += BK) {
-        __syncthreads();  // the previous tile is consumed (first pass: nothing to wait for but harmless)
+        __syncthreads();  // the previous tile is consumed
         const int nk = min(BK, j_hi - jt + 1);
         if (tid < BK) ksrc[tid] = tid < nk ? key_source(a, jt + tid, p0) : -1;
         __syncthreads();
-        for (int idx = tid; idx < BK * Dk; idx += ATT_THREADS) {
-            const int r = idx / Dk, d = idx - r * Dk;
+        stage_rows<CT>(Ks, Dkp, BK, Dk, [&](int r) -> const CT* {
             const int s = ksrc[r];
-            float v = 0.f;
-            if (s >= 0) v = ldf(kc, ((size_t)g * a.L + s) * Dk + d);
-            else if (s <= -2) v = ldf(kn, ((size_t)(-s - 2) * a.G + g) * Dk + d);
-            Ks[r * Dkp + d] = v;
-        }
-        for (int idx = tid; idx < BK * DVW; idx += ATT_THREADS) {
-            const int r = idx / DVW, c = idx - r * DVW;
+            return s >= 0 ? kc + ((size_t)g * a.L + s) * Dk : (s <= -2 ? kn + ((size_t)(-s - 2) * a.G + g) * Dk : nullptr);
+        }, tid, ATT_THREADS);
+        stage_rows<CT>(Vs, DVW, BK, Dv, [&](int r) -> const CT* {
             const int s = ksrc[r];
-            float v = 0.f;
-            if (c < Dv) {
-                if (s >= 0) v = ldf(vc, ((size_t)g * a.L + s) * Dv + c);
-                else if (s <= -2) v = ldf(vn, ((size_t)(-s - 2) * a.G + g) * Dv + c);
-            }
-            Vs[r * DVW + c] = v;
-        }
+            return s >= 0 ? vc + ((size_t)g * a.L + s) * Dv : (s <= -2 ? vn + ((size_t)(-s - 2) * a.G + g) * Dv : nullptr);
+        }, tid, ATT_THREADS);
         __syncthreads();
 
-        float s[4][4];
+        float s[4][2];
 #pragma unroll
-        for (int r = 0; r < 4; ++r)
+        for (int r = 0; r < 4; ++r) s[r][0] = s[r][1] = 0.f;
+        const float4* q4 = reinterpret_cast<const float4*>(Qs + (ty * 4) * Dkp);
+        const float4* k4 = reinterpret_cast<const float4*>(Ks + tx * Dkp);
+        const int rs4 = Dkp / 4;
+#pragma unroll 2
+        for (int d = 0; d < Dk4; ++d) {
+            float4 qv[4], kv[2];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) s[r][c] = 0.f;
-        for (int d = 0; d < Dk; ++d) {
-            float qv[4], kv[4];
-#pragma unroll
-            for (int r = 0; r < 4; ++r) qv[r] = Qs[(ty * 4 + r) * Dkp + d];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) kv[c] = Ks[(tx + 16 * c) * Dkp + d];
+            for (int r = 0; r < 4; ++r) qv[r] = q4[r * rs4 + d];
+            kv[0] = k4[d];
+            kv[1] = k4[16 * rs4 + d];
 #pragma unroll
             for (int r = 0; r < 4; ++r)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) s[r][c] = fmaf(qv[r], kv[c], s[r][c]);
+                for (int c = 0; c < 2; ++c) {
+                    s[r][c] = fmaf(qv[r].x, kv[c].x, s[r][c]);
+                    s[r][c] = fmaf(qv[r].y, kv[c].y, s[r][c]);
+                    s[r][c] = fmaf(qv[r].z, kv[c].z, s[r][c]);
+                    s[r][c] = fmaf(qv[r].w, kv[c].w, s[r][c]);
+                }
         }
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
@@ -214,7 +272,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_chunk_kernel(const CcSeqAttn
             const int i = p0 + i0 + qi;
             float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 const int col = tx + 16 * c;
                 const int j = jt + col;
                 const bool ok = qi < nq && col < nk && ksrc[col] != -1 && j <= i && (a.window == 0 || i - j < a.window);
@@ -225,31 +283,43 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_chunk_kernel(const CcSeqAttn
             for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
             const float m_new = fmaxf(m[r], mx);
             const float corr = (m[r] == -INFINITY) ? 0.f : expf(m[r] - m_new);
-            float rs = 0.f;
+            float rsum = 0.f;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 const float pr = (s[r][c] == -INFINITY) ? 0.f : expf(s[r][c] - m_new);
-                rs += pr;
+                rsum += pr;
                 Ss[qi * SP + tx + 16 * c] = pr;
             }
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o);
-            l[r] = l[r] * corr + rs;
+            for (int o = 8; o > 0; o >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
+            l[r] = l[r] * corr + rsum;
             m[r] = m_new;
 #pragma unroll
-            for (int c = 0; c < DVT; ++c) O[r][c] *= corr;
+            for (int c = 0; c < 4 * DV4; ++c) O[r][c] *= corr;
         }
         __syncwarp();
-        for (int k = 0; k < nk; ++k) {
-            float pv[4], vv[DVT];
+        const float4* p4 = reinterpret_cast<const float4*>(Ss + (ty * 4) * SP);
+        const float4* v4 = reinterpret_cast<const float4*>(Vs) + tx;
+#pragma unroll 2
+        for (int kq = 0; kq < BK / 4; ++kq) {
+            float4 pv[4];
 #pragma unroll
-            for (int r = 0; r < 4; ++r) pv[r] = Ss[(ty * 4 + r) * SP + k];
+            for (int r = 0; r < 4; ++r) pv[r] = p4[r * (SP / 4) + kq];
 #pragma unroll
-            for (int c = 0; c < DVT; ++c) vv[c] = Vs[k * DVW + tx + 16 * c];
+            for (int kk = 0; kk < 4; ++kk) {
 #pragma unroll
-            for (int r = 0; r < 4; ++r)
+                for (int c = 0; c < DV4; ++c) {
+                    const float4 vv = v4[(kq * 4 + kk) * (DVW / 4) + 16 * c];
 #pragma unroll
-                for (int c = 0; c < DVT; ++c) O[r][c] = fmaf(pv[r], vv[c], O[r][c]);
+                    for (int r = 0; r < 4; ++r) {
+                        const float pk = kk == 0 ? pv[r].x : kk == 1 ? pv[r].y : kk == 2 ? pv[r].z : pv[r].w;
+                        O[r][4 * c + 0] = fmaf(pk, vv.x, O[r][4 * c + 0]);
+                        O[r][4 * c + 1] = fmaf(pk, vv.y, O[r][4 * c + 1]);
+                        O[r][4 * c + 2] = fmaf(pk, vv.z, O[r][4 * c + 2]);
+                        O[r][4 * c + 3] = fmaf(pk, vv.w, O[r][4 * c + 3]);
+                    }
+                }
+            }
         }
     }
     YT* y = (YT*)a.y;
@@ -259,19 +329,22 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_chunk_kernel(const CcSeqAttn
         if (qi >= nq) continue;
         const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
 #pragma unroll
-        for (int c = 0; c < DVT; ++c) {
-            const int col = tx + 16 * c;
+        for (int c = 0; c < 4 * DV4; ++c) {
+            const int col = 64 * (c / 4) + 4 * tx + (c & 3);
             if (col < Dv) stf(y, ((size_t)(i0 + qi) * a.H + h) * Dv + col, O[r][c] * inv);
         }
     }
 }
 
 // ------------------------------------------------------------------------------------------------ decode attention
-constexpr int KS = 256;  // keys per CTA
+constexpr int KS = 64;            // keys per CTA of the one-token kernel
+constexpr int DEC_THREADS = 128;  // two threads per key
+constexpr int DEC_MAX_SPLITS = 32;  // runs of tiles per key/value head: bounds the partials the last CTA combines
 
 __host__ __device__ inline int decode_max_splits(int L, int window) {
     const long long maxkeys = window > 0 ? (window < L + 1 ? window : L + 1) : (long long)L + 1;
-    return (int)((maxkeys + KS - 1) / KS);
+    const long long tiles = (maxkeys + KS - 1) / KS;
+    return (int)(tiles < DEC_MAX_SPLITS ? tiles : DEC_MAX_SPLITS);
 }
 
 template <typename CT>
@@ -293,20 +366,31 @@ __device__ __forceinline__ void append_row(const CcSeqAttn& a, int g, int t, int
     }
 }
 
-template <typename CT, typename YT>
-__global__ void __launch_bounds__(KS) attn_decode_kernel(const CcSeqAttn a) {
+// One CTA = a run of 64-key tiles of one key/value head, all R = H / G query heads of the group.  Per tile: K and V
+// rows staged once into shared memory as fp32 (16-byte loads, four in flight per thread), scores by two threads per
+// key, online softmax per query head, the weighted value sum by one thread per value column.  A head's keys are cut
+// into at most DEC_MAX_SPLITS runs; partial (max, sum, weighted values) go to the workspace; the last CTA of the head to
+// arrive combines them in split order and, when asked, appends the new row.
+template <typename CT, typename YT, int RMAX>
+__global__ void __launch_bounds__(DEC_THREADS) attn_decode_kernel(const CcSeqAttn a) {
     extern __shared__ float sm[];
     const int R = a.H / a.G, Dk = a.Dk, Dv = a.Dv;
-    float* qs = sm;             // [R, Dk]
-    float* S = qs + R * Dk;     // [R, KS]
-    int* ksrc = (int*)(S + R * KS);
+    const int Dkp = Dk + ((2 - (Dk & 3)) & 3);  // = 2 (mod 4): the 16 key rows x 2 interleaved halves a warp reads fall in 32 banks
+    float* qs = sm;               // [R, Dk]
+    float* Ks = qs + R * Dk;      // [KS, Dkp]
+    float* Vs = Ks + KS * Dkp;    // [KS, Dv]
+    float* Ps = Vs + KS * Dv;     // [R, KS]
+    int* ksrc = (int*)(Ps + R * KS);
     __shared__ int s_last;
+    __shared__ float s_M[16], s_L[16], s_corr[16];
 
     const int sp = blockIdx.x, g = blockIdx.y, tid = threadIdx.x;
     const int p = a.input_pos[0];
     const int j_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
     const int n = p - j_lo + 1;
-    const int nsplit = (n + KS - 1) / KS;
+    const int n_tiles = (n + KS - 1) / KS;
+    const int tiles_per = (n_tiles + DEC_MAX_SPLITS - 1) / DEC_MAX_SPLITS;
+    const int nsplit = (n_tiles + tiles_per - 1) / tiles_per;
     if (sp >= nsplit) return;
     const int NS = decode_max_splits(a.L, a.window);
     int* counters = (int*)a.workspace;
@@ -318,52 +402,99 @@ __global__ void __launch_bounds__(KS) attn_decode_kernel(const CcSeqAttn a) {
     const CT* vc = (const CT*)a.v_cache;
     const CT* kn = (const CT*)a.k_new;
     const CT* vn = (const CT*)a.v_new;
-    for (int i = tid; i < R * Dk; i += KS) qs[i] = a.q[(size_t)g * R * Dk + i];
-    const int j = j_lo + sp * KS + tid;
-    int src = -1;
-    if (j <= p) src = key_source(a, j, p);
-    ksrc[tid] = src;
-    __syncthreads();
-    const int nk = min(KS, p - (j_lo + sp * KS) + 1);
-
-    if (src != -1) {
-        const CT* krow = src >= 0 ? kc + ((size_t)g * a.L + src) * Dk : kn + (size_t)g * Dk;
-        for (int r = 0; r < R; ++r) {
-            float acc = 0.f;
-            for (int d = 0; d < Dk; ++d) acc = fmaf(qs[r * Dk + d], ldf(krow, d), acc);
-            S[r * KS + tid] = acc * a.scale;
-        }
-    } else {
-        for (int r = 0; r < R; ++r) S[r * KS + tid] = -INFINITY;
-    }
-    __syncthreads();
+    for (int i = tid; i < R * Dk; i += DEC_THREADS) qs[i] = a.q[(size_t)g * R * Dk + i];
+    if (tid < 16) { s_M[tid] = -INFINITY; s_L[tid] = 0.f; }
     const int warp = tid >> 5, lane = tid & 31;
-    const size_t pbase = ((size_t)g * NS + sp) * R;
-    for (int r = warp; r < R; r += KS / 32) {
-        float mx = -INFINITY;
-        for (int k = lane; k < KS; k += 32) mx = fmaxf(mx, S[r * KS + k]);
-        mx = warp_max(mx);
-        float sum = 0.f;
-        for (int k = lane; k < KS; k += 32) {
-            const float sv = S[r * KS + k];
-            const float pr = sv == -INFINITY ? 0.f : expf(sv - mx);
-            S[r * KS + k] = pr;
-            sum += pr;
+    float oacc[2][RMAX];   // value columns tid and tid + DEC_THREADS
+#pragma unroll
+    for (int r = 0; r < RMAX; ++r) oacc[0][r] = oacc[1][r] = 0.f;
+
+    const int tile_end = min(n_tiles, (sp + 1) * tiles_per);
+    for (int tile = sp * tiles_per; tile < tile_end; ++tile) {
+        const int j0 = j_lo + tile * KS;
+        const int nk = min(KS, p - j0 + 1);
+        __syncthreads();   // the previous tile is consumed (first pass: qs and the running maxima are written)
+        if (tid < KS) ksrc[tid] = tid < nk ? key_source(a, j0 + tid, p) : -1;
+        __syncthreads();
+        stage_rows<CT>(Ks, Dkp, nk, Dk, [&](int r) -> const CT* {
+            const int s = ksrc[r];
+            return s >= 0 ? kc + ((size_t)g * a.L + s) * Dk : (s <= -2 ? kn + (size_t)g * Dk : nullptr);
+        }, tid, DEC_THREADS);
+        stage_rows<CT>(Vs, Dv, nk, Dv, [&](int r) -> const CT* {
+            const int s = ksrc[r];
+            return s >= 0 ? vc + ((size_t)g * a.L + s) * Dv : (s <= -2 ? vn + (size_t)g * Dv : nullptr);
+        }, tid, DEC_THREADS);
+        __syncthreads();
+        {   // scores: threads 2k and 2k+1 take the even and the odd elements of key k
+            const int key = tid >> 1, half = tid & 1;
+            float acc[RMAX];
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r) acc[r] = 0.f;
+            if (key < nk) {
+                const float* kr = Ks + key * Dkp;
+#pragma unroll 4
+                for (int d = half; d < Dk; d += 2) {
+                    const float kv = kr[d];
+#pragma unroll
+                    for (int r = 0; r < RMAX; ++r)
+                        if (r < R) acc[r] = fmaf(qs[r * Dk + d], kv, acc[r]);
+                }
+            }
+            const bool ok = key < nk && ksrc[key] != -1;
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r) {
+                const float tot = acc[r] + __shfl_xor_sync(0xffffffffu, acc[r], 1);
+                if (r < R && half == 0) Ps[r * KS + key] = ok ? tot * a.scale : -INFINITY;
+            }
         }
-        sum = warp_sum(sum);
-        if (lane == 0) { part_m[pbase + r] = mx; part_l[pbase + r] = sum; }
+        __syncthreads();
+        for (int r = warp; r < R; r += DEC_THREADS / 32) {
+            float mx = -INFINITY;
+            for (int k = lane; k < KS; k += 32) mx = fmaxf(mx, Ps[r * KS + k]);
+            mx = warp_max(mx);
+            const float m_old = s_M[r];
+            const float m_new = fmaxf(m_old, mx);
+            float sum = 0.f;
+            for (int k = lane; k < KS; k += 32) {
+                const float sv = Ps[r * KS + k];
+                const float pr = sv == -INFINITY ? 0.f : expf(sv - m_new);
+                Ps[r * KS + k] = pr;
+                sum += pr;
+            }
+            sum = warp_sum(sum);
+            if (lane == 0) {
+                const float corr = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+                s_corr[r] = corr;
+                s_L[r] = s_L[r] * corr + sum;
+                s_M[r] = m_new;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+            const int c = tid + cc * DEC_THREADS;
+            if (c >= Dv) break;
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r)
+                if (r < R) oacc[cc][r] *= s_corr[r];
+#pragma unroll 4
+            for (int k = 0; k < nk; ++k) {
+                const float v = Vs[k * Dv + c];
+#pragma unroll
+                for (int r = 0; r < RMAX; ++r)
+                    if (r < R) oacc[cc][r] = fmaf(Ps[r * KS + k], v, oacc[cc][r]);
+            }
+        }
     }
-    __syncthreads();
-    for (int idx = tid; idx < R * Dv; idx += KS) {
-        const int r = idx / Dv, c = idx - r * Dv;
-        float acc = 0.f;
-        for (int k = 0; k < nk; ++k) {
-            const int s = ksrc[k];
-            if (s == -1) continue;
-            const float v = s >= 0 ? ldf(vc, ((size_t)g * a.L + s) * Dv + c) : ldf(vn, (size_t)g * Dv + c);
-            acc = fmaf(S[r * KS + k], v, acc);
-        }
-        part_o[(pbase + r) * Dv + c] = acc;
+    const size_t pbase = ((size_t)g * NS + sp) * R;
+    if (tid < R) { part_m[pbase + tid] = s_M[tid]; part_l[pbase + tid] = s_L[tid]; }
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+        const int c = tid + cc * DEC_THREADS;
+        if (c >= Dv) break;
+#pragma unroll
+        for (int r = 0; r < RMAX; ++r)
+            if (r < R) part_o[(pbase + r) * Dv + c] = oacc[cc][r];
     }
     __threadfence();
     __syncthreads();
@@ -372,31 +503,60 @@ __global__ void __launch_bounds__(KS) attn_decode_kernel(const CcSeqAttn a) {
     if (!s_last) return;
     __threadfence();
     // the last CTA of this head: every other CTA of the head has finished reading; combine in split order
+    // (partials are read with ld.global.cg: other SMs wrote them, so L1 is bypassed)
     YT* y = (YT*)a.y;
-    const volatile float* vm = part_m;
-    const volatile float* vl = part_l;
-    const volatile float* vo = part_o;
-    for (int idx = tid; idx < R * Dv; idx += KS) {
-        const int r = idx / Dv, c = idx - r * Dv;
+    __shared__ float s_inv[16], s_max[16];
+    float* wgt = Ps;   // [R, KS] weights of up to KS splits at a time (reuses the probability tile)
+    for (int r = warp; r < R; r += DEC_THREADS / 32) {
         const int h = g * R + r;
-        float M = -INFINITY, Lsum = 0.f;
+        float M = -INFINITY;
         if (a.sink_mode == CC_SINK_LEARNED) M = a.sink[h];
         else if (a.sink_mode == CC_SINK_ZERO) M = 0.f;
         const float sinkv = M;
-        for (int s = 0; s < nsplit; ++s) M = fmaxf(M, vm[((size_t)g * NS + s) * R + r]);
-        if (a.sink_mode != CC_SINK_NONE) Lsum = expf(sinkv - M);
-        float acc = 0.f;
-        for (int s = 0; s < nsplit; ++s) {
+        for (int s = lane; s < nsplit; s += 32) M = fmaxf(M, __ldcg(part_m + ((size_t)g * NS + s) * R + r));
+        M = warp_max(M);
+        float Lsum = 0.f;
+        for (int s = lane; s < nsplit; s += 32) {
             const size_t b = ((size_t)g * NS + s) * R + r;
-            const float ms = vm[b];
-            const float w = ms == -INFINITY ? 0.f : expf(ms - M);
-            Lsum += vl[b] * w;
-            acc += vo[b * Dv + c] * w;
+            const float ms = __ldcg(part_m + b);
+            Lsum += __ldcg(part_l + b) * (ms == -INFINITY ? 0.f : expf(ms - M));
         }
-        stf(y, (size_t)h * Dv + c, Lsum > 0.f ? acc / Lsum : 0.f);
+        Lsum = warp_sum(Lsum);
+        if (a.sink_mode != CC_SINK_NONE) Lsum += expf(sinkv - M);
+        if (lane == 0) { s_inv[r] = Lsum > 0.f ? 1.0f / Lsum : 0.f; s_max[r] = M; }
+    }
+    for (int c0 = 0; c0 < Dv; c0 += DEC_THREADS) {
+        const int c = c0 + tid;
+        float acc[RMAX];
+#pragma unroll
+        for (int r = 0; r < RMAX; ++r) acc[r] = 0.f;
+        for (int s0 = 0; s0 < nsplit; s0 += KS) {   // splits in order, KS at a time
+            const int ns = min(KS, nsplit - s0);
+            __syncthreads();
+            for (int i = tid; i < R * ns; i += DEC_THREADS) {
+                const int r = i / ns, s = i - r * ns;
+                const float ms = __ldcg(part_m + ((size_t)g * NS + s0 + s) * R + r);
+                wgt[r * KS + s] = ms == -INFINITY ? 0.f : expf(ms - s_max[r]);
+            }
+            __syncthreads();
+            if (c < Dv) {
+#pragma unroll 8
+                for (int s = 0; s < ns; ++s) {
+                    const float* po = part_o + (((size_t)g * NS + s0 + s) * R) * Dv + c;
+#pragma unroll
+                    for (int r = 0; r < RMAX; ++r)
+                        if (r < R) acc[r] = fmaf(__ldcg(po + (size_t)r * Dv), wgt[r * KS + s], acc[r]);
+                }
+            }
+        }
+        if (c < Dv) {
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r)
+                if (r < R) stf(y, (size_t)(g * R + r) * Dv + c, acc[r] * s_inv[r]);
+        }
     }
     if (tid == 0) counters[g] = 0;
-    if (a.append) append_row<CT>(a, g, 0, p, tid, KS);
+    if (a.append) append_row<CT>(a, g, 0, p, tid, DEC_THREADS);
 }
 
 template <typename CT>
@@ -462,11 +622,11 @@ static int check_attn(const CcSeqAttn* a) {
     return CC_SEQ_OK;
 }
 
-template <typename CT, typename YT, int DVT>
+template <typename CT, typename YT, int DV4>
 static int launch_chunk(const CcSeqAttn* a, cudaStream_t st) {
-    const int Dkp = a->Dk | 1;
-    const size_t smem = sizeof(float) * ((size_t)BQ * Dkp + (size_t)BK * Dkp + (size_t)BK * 16 * DVT + (size_t)BQ * (BK + 1)) + sizeof(int) * BK;
-    auto kern = attn_chunk_kernel<CT, YT, DVT>;
+    const int Dkp = vec_stride(a->Dk);
+    const size_t smem = sizeof(float) * ((size_t)(BQ + BK) * Dkp + (size_t)BK * 64 * DV4 + (size_t)BQ * (BK + 4)) + sizeof(int) * BK;
+    auto kern = attn_chunk_kernel<CT, YT, DV4>;
     static size_t configured = 48 * 1024;
     if (smem > configured) {
         configured = smem;
@@ -480,21 +640,19 @@ static int launch_chunk(const CcSeqAttn* a, cudaStream_t st) {
 
 template <typename CT, typename YT>
 static int dispatch_chunk(const CcSeqAttn* a, cudaStream_t st) {
-    const int need = (a->Dv + 15) / 16;
+    const int need = (a->Dv + 63) / 64;
     if (need <= 1) return launch_chunk<CT, YT, 1>(a, st);
     if (need <= 2) return launch_chunk<CT, YT, 2>(a, st);
     if (need <= 3) return launch_chunk<CT, YT, 3>(a, st);
-    if (need <= 4) return launch_chunk<CT, YT, 4>(a, st);
-    if (need <= 6) return launch_chunk<CT, YT, 6>(a, st);
-    if (need <= 8) return launch_chunk<CT, YT, 8>(a, st);
-    return launch_chunk<CT, YT, 16>(a, st);
+    return launch_chunk<CT, YT, 4>(a, st);
 }
 
-template <typename CT, typename YT>
-static int launch_decode(const CcSeqAttn* a, cudaStream_t st) {
+template <typename CT, typename YT, int RMAX>
+static int launch_decode_r(const CcSeqAttn* a, cudaStream_t st) {
     const int R = a->H / a->G;
-    const size_t smem = sizeof(float) * ((size_t)R * a->Dk + (size_t)R * KS) + sizeof(int) * KS;
-    auto kern = attn_decode_kernel<CT, YT>;
+    const int Dkp = a->Dk + ((2 - (a->Dk & 3)) & 3);
+    const size_t smem = sizeof(float) * ((size_t)R * a->Dk + (size_t)KS * Dkp + (size_t)KS * a->Dv + (size_t)R * KS) + sizeof(int) * KS;
+    auto kern = attn_decode_kernel<CT, YT, RMAX>;
     static size_t configured = 48 * 1024;
     if (smem > configured) {
         configured = smem;
@@ -502,8 +660,19 @@ static int launch_decode(const CcSeqAttn* a, cudaStream_t st) {
         if (e != cudaSuccess) return fail(CC_SEQ_ERR_CUDA, cudaGetErrorString(e));
     }
     dim3 grid(decode_max_splits(a->L, a->window), a->G);
-    kern<<<grid, KS, smem, st>>>(*a);
+    kern<<<grid, DEC_THREADS, smem, st>>>(*a);
     return cuda_check("attn_decode_kernel");
+}
+
+template <typename CT, typename YT>
+static int launch_decode(const CcSeqAttn* a, cudaStream_t st) {
+    const int R = a->H / a->G;
+    if (R <= 1) return launch_decode_r<CT, YT, 1>(a, st);
+    if (R <= 2) return launch_decode_r<CT, YT, 2>(a, st);
+    if (R <= 4) return launch_decode_r<CT, YT, 4>(a, st);
+    if (R <= 8) return launch_decode_r<CT, YT, 8>(a, st);
+    if (R <= 16) return launch_decode_r<CT, YT, 16>(a, st);
+    return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "attention_decode: more than 16 query heads per key/value head");
 }
 
 #define CCS_DISPATCH2(d0, d1, CALL)                                                              \
