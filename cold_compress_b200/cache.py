@@ -235,7 +235,7 @@ class KVCache(nn.Module):
         addressed by position: q [T, Hq, Dk] fp32 (normalised), k_new [T, H, Dk] / v_new [T, H, Dv] in the cache's
         dtype, input_pos int32 [1] = position of the first token (device), y [T, Hq, Dv] out.  Query p sees key j
         when j <= p and (window == 0 or p - j < window).  T == 1 is one launch (keys split over CTAs, append fused);
-        T > 1 is the tiled chunk kernel followed by the append kernel.  Nothing here synchronises with the host."""
+        T > 1 (and groups of more than 16 query heads) is the tiled chunk kernel followed by the append kernel.  Nothing here synchronises with the host."""
         from . import seq_ops
         keep = self.sequence_window()
         if keep is None or self.quantize:
@@ -245,7 +245,7 @@ class KVCache(nn.Module):
         T = q.shape[0]
         args = (q, k_new, v_new, self.k_cache, self.v_cache, self.pos, self.mask, self.cache_cts, input_pos, y, sink,
                 int(window), int(sink_mode), float(scale))
-        if T == 1:
+        if T == 1 and q.shape[1] <= 16 * self.n_heads:   # the one-token kernel holds up to 16 query heads per KV head
             seq_ops.seq_attention(*args, seq_ops.ATTN_DECODE_APPEND, self._sequence_workspace(q.shape[1], window))
         else:
             seq_ops.seq_attention(*args, seq_ops.ATTN_CHUNK, None)

@@ -335,15 +335,18 @@ def test_long_decoding_through_rings_and_splits():
     ([window_layer(2, heads=12, kv_heads=3, dim=130, vdim=70, ff=300, limit=0.3), global_layer(heads=12, kv_heads=12, dim=48, vdim=17, every=1000, coef=2.0, ff=0, v_mix=False)],
      dict(width=200, vocab=1000, alpha=0.5, eps=1e-2, scale=0.1, bigram=None)),
     ([global_layer(v_mix=False), window_layer(5), window_layer(6)], dict(width=33, vocab=17, bigram=(1009, 1000003, 999983))),
-], ids=["all_ones", "wide_heads_no_bigram", "odd_width_big_hash"])
-def test_other_sizes(layers, kw):
+    ([global_layer(heads=34, kv_heads=2, dim=8, vdim=4, ff=30), window_layer(3, heads=17, kv_heads=1, dim=12, vdim=8, ff=0)],
+     dict(width=51, vocab=77)),
+], ids=["all_ones", "wide_heads_no_bigram", "odd_width_big_hash", "seventeen_query_heads_per_kv_head"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_other_sizes(layers, kw, dtype):
     cfg = make_config(layers, **kw)
     W = random_weights(cfg, seed=15)
     tokens = torch.randint(0, cfg["vocab"], (29,), generator=torch.Generator().manual_seed(16)).tolist()
     want = _reference_logits(cfg, W, tokens)
-    model = build_model(cfg, W, torch.float32, 32)
+    model = build_model(cfg, W, dtype, 32)
     got = _run_portions(model, tokens, (5, 1, 1, 20, 2))
-    assert row_error(got, want).max() < fp32_tolerance(cfg, W, tokens, want), row_error(got, want).max()
+    assert row_error(got, want).max() < _tol(dtype, cfg, W, tokens, want), row_error(got, want).max()
 
 
 def test_checkpoint_folder_generate_and_graphed_decoder(tmp_path):
