@@ -337,9 +337,17 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_chunk_kernel(const CcSeqAttn
 }
 
 // ------------------------------------------------------------------------------------------------ decode attention
-constexpr int KS = 64;            // keys per CTA of the one-token kernel
-constexpr int DEC_THREADS = 128;  // two threads per key
-constexpr int DEC_MAX_SPLITS = 32;  // runs of tiles per key/value head: bounds the partials the last CTA combines
+constexpr int KS = 128;           // keys per tile of the one-token kernel
+constexpr int DEC_THREADS = 128;  // one thread per key
+#ifndef CC_DEC_MAX_SPLITS
+#define CC_DEC_MAX_SPLITS 64
+#endif
+constexpr int DEC_MAX_SPLITS = CC_DEC_MAX_SPLITS;  // runs of tiles per key/value head: bounds the partials the last CTA combines
+
+__host__ __device__ inline int dec_k_stride(int Dk) {
+    const int d4 = (Dk + 3) & ~3;
+    return d4 + ((8 - (d4 & 31)) & 31);
+}
 
 __host__ __device__ inline int decode_max_splits(int L, int window) {
     const long long maxkeys = window > 0 ? (window < L + 1 ? window : L + 1) : (long long)L + 1;
@@ -366,20 +374,22 @@ __device__ __forceinline__ void append_row(const CcSeqAttn& a, int g, int t, int
     }
 }
 
-// One CTA = a run of 64-key tiles of one key/value head, all R = H / G query heads of the group.  Per tile: K and V
-// rows staged once into shared memory as fp32 (16-byte loads, four in flight per thread), scores by two threads per
-// key, online softmax per query head, the weighted value sum by one thread per value column.  A head's keys are cut
-// into at most DEC_MAX_SPLITS runs; partial (max, sum, weighted values) go to the workspace; the last CTA of the head to
-// arrive combines them in split order and, when asked, appends the new row.
+// One CTA = a run of KS-key tiles of one key/value head, all R = H / G query heads of the group.  Per tile: one thread
+// per key reads its K row straight from global memory with 16-byte loads (all in flight at once; consecutive keys are
+// consecutive rows, so a warp's loads cover whole lines) and dots it with the R query rows held in shared memory
+// (broadcast float4 reads); online softmax per query head; then one thread per value column walks the tile's V rows
+// (coalesced across the columns).  A head's keys are cut into at most DEC_MAX_SPLITS runs; partial (max, sum, weighted
+// values) go to the workspace; the last CTA of the head to arrive combines them in split order and, when asked,
+// appends the new row.
 template <typename CT, typename YT, int RMAX>
 __global__ void __launch_bounds__(DEC_THREADS) attn_decode_kernel(const CcSeqAttn a) {
-    extern __shared__ float sm[];
+    extern __shared__ float4 smd4[];
+    float* sm = reinterpret_cast<float*>(smd4);
+    constexpr int VEC = 16 / (int)sizeof(CT);
     const int R = a.H / a.G, Dk = a.Dk, Dv = a.Dv;
-    const int Dkp = Dk + ((2 - (Dk & 3)) & 3);  // = 2 (mod 4): the 16 key rows x 2 interleaved halves a warp reads fall in 32 banks
-    float* qs = sm;               // [R, Dk]
-    float* Ks = qs + R * Dk;      // [KS, Dkp]
-    float* Vs = Ks + KS * Dkp;    // [KS, Dv]
-    float* Ps = Vs + KS * Dv;     // [R, KS]
+    const int Dq = (Dk + 7) & ~7;   // q rows zero-padded to whole vectors
+    float* qs = sm;               // [R, Dq]
+    float* Ps = qs + R * Dq;      // [R, KS]
     int* ksrc = (int*)(Ps + R * KS);
     __shared__ int s_last;
     __shared__ float s_M[16], s_L[16], s_corr[16];
@@ -402,50 +412,77 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_decode_kernel(const CcSeqAtt
     const CT* vc = (const CT*)a.v_cache;
     const CT* kn = (const CT*)a.k_new;
     const CT* vn = (const CT*)a.v_new;
-    for (int i = tid; i < R * Dk; i += DEC_THREADS) qs[i] = a.q[(size_t)g * R * Dk + i];
+    for (int i = tid; i < R * Dq; i += DEC_THREADS) {
+        const int r = i / Dq, d = i - r * Dq;
+        qs[i] = d < Dk ? a.q[((size_t)g * R + r) * Dk + d] : 0.f;
+    }
     if (tid < 16) { s_M[tid] = -INFINITY; s_L[tid] = 0.f; }
     const int warp = tid >> 5, lane = tid & 31;
     float oacc[2][RMAX];   // value columns tid and tid + DEC_THREADS
 #pragma unroll
     for (int r = 0; r < RMAX; ++r) oacc[0][r] = oacc[1][r] = 0.f;
+    const bool vec_rows = (Dk % VEC) == 0;
+    // value phase with 16-byte loads when the rows allow it and R x VEC accumulators fit in registers
+    constexpr int VR = RMAX * VEC <= 64 ? RMAX : 1;
+    const int ncg = Dv / VEC;
+    const bool vec_values = RMAX * VEC <= 64 && Dv % VEC == 0 && ncg <= DEC_THREADS;
+    const int nkg = vec_values ? DEC_THREADS / ncg : 1;
+    const int kg = vec_values ? tid / ncg : 0, cg = vec_values ? tid - kg * ncg : 0;
+    float vacc[VR][VEC];
+#pragma unroll
+    for (int r = 0; r < VR; ++r)
+#pragma unroll
+        for (int x = 0; x < VEC; ++x) vacc[r][x] = 0.f;
 
     const int tile_end = min(n_tiles, (sp + 1) * tiles_per);
     for (int tile = sp * tiles_per; tile < tile_end; ++tile) {
         const int j0 = j_lo + tile * KS;
         const int nk = min(KS, p - j0 + 1);
         __syncthreads();   // the previous tile is consumed (first pass: qs and the running maxima are written)
-        if (tid < KS) ksrc[tid] = tid < nk ? key_source(a, j0 + tid, p) : -1;
-        __syncthreads();
-        stage_rows<CT>(Ks, Dkp, nk, Dk, [&](int r) -> const CT* {
-            const int s = ksrc[r];
-            return s >= 0 ? kc + ((size_t)g * a.L + s) * Dk : (s <= -2 ? kn + (size_t)g * Dk : nullptr);
-        }, tid, DEC_THREADS);
-        stage_rows<CT>(Vs, Dv, nk, Dv, [&](int r) -> const CT* {
-            const int s = ksrc[r];
-            return s >= 0 ? vc + ((size_t)g * a.L + s) * Dv : (s <= -2 ? vn + (size_t)g * Dv : nullptr);
-        }, tid, DEC_THREADS);
-        __syncthreads();
-        {   // scores: threads 2k and 2k+1 take the even and the odd elements of key k
-            const int key = tid >> 1, half = tid & 1;
+        const int src = tid < nk ? key_source(a, j0 + tid, p) : -1;
+        ksrc[tid] = src;
+        {   // scores: one thread per key
             float acc[RMAX];
 #pragma unroll
             for (int r = 0; r < RMAX; ++r) acc[r] = 0.f;
-            if (key < nk) {
-                const float* kr = Ks + key * Dkp;
-#pragma unroll 4
-                for (int d = half; d < Dk; d += 2) {
-                    const float kv = kr[d];
+            if (src != -1) {
+                const CT* krow = src >= 0 ? kc + ((size_t)g * a.L + src) * Dk : kn + (size_t)g * Dk;
+                if (vec_rows) {
+                    const uint4* k16 = reinterpret_cast<const uint4*>(krow);
+                    const float4* q4 = reinterpret_cast<const float4*>(qs);
+                    const int nv = Dk / VEC, q4_row = Dq / 4;
+#pragma unroll 8
+                    for (int i = 0; i < nv; ++i) {
+                        const uint4 u = __ldg(k16 + i);
+                        const CT* e = reinterpret_cast<const CT*>(&u);
+                        float kf[VEC];
 #pragma unroll
-                    for (int r = 0; r < RMAX; ++r)
-                        if (r < R) acc[r] = fmaf(qs[r * Dk + d], kv, acc[r]);
+                        for (int x = 0; x < VEC; ++x) kf[x] = ldf(e, x);
+#pragma unroll
+                        for (int r = 0; r < RMAX; ++r)
+                            if (r < R) {
+#pragma unroll
+                                for (int x4 = 0; x4 < VEC / 4; ++x4) {
+                                    const float4 qv = q4[r * q4_row + i * (VEC / 4) + x4];
+                                    acc[r] = fmaf(qv.x, kf[4 * x4 + 0], acc[r]);
+                                    acc[r] = fmaf(qv.y, kf[4 * x4 + 1], acc[r]);
+                                    acc[r] = fmaf(qv.z, kf[4 * x4 + 2], acc[r]);
+                                    acc[r] = fmaf(qv.w, kf[4 * x4 + 3], acc[r]);
+                                }
+                            }
+                    }
+                } else {
+                    for (int d = 0; d < Dk; ++d) {
+                        const float kv = ldf(krow, d);
+#pragma unroll
+                        for (int r = 0; r < RMAX; ++r)
+                            if (r < R) acc[r] = fmaf(qs[r * Dq + d], kv, acc[r]);
+                    }
                 }
             }
-            const bool ok = key < nk && ksrc[key] != -1;
 #pragma unroll
-            for (int r = 0; r < RMAX; ++r) {
-                const float tot = acc[r] + __shfl_xor_sync(0xffffffffu, acc[r], 1);
-                if (r < R && half == 0) Ps[r * KS + key] = ok ? tot * a.scale : -INFINITY;
-            }
+            for (int r = 0; r < RMAX; ++r)
+                if (r < R) Ps[r * KS + tid] = src != -1 ? acc[r] * a.scale : -INFINITY;
         }
         __syncthreads();
         for (int r = warp; r < R; r += DEC_THREADS / 32) {
@@ -470,20 +507,92 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_decode_kernel(const CcSeqAtt
             }
         }
         __syncthreads();
+        if (vec_values) {
+            // thread (kg, cg): keys kg, kg + nkg, ... of the tile x the VEC value columns of group cg, 16-byte loads
+            if (kg < nkg) {
+#pragma unroll
+                for (int r = 0; r < VR; ++r)
+                    if (r < R) {
+                        const float cr = s_corr[r];
+#pragma unroll
+                        for (int x = 0; x < VEC; ++x) vacc[r][x] *= cr;
+                    }
+                const CT* vbase = vc + (size_t)g * a.L * Dv + cg * VEC;
+                const CT* vnew = vn + (size_t)g * Dv + cg * VEC;
+#pragma unroll 4
+                for (int k = kg; k < nk; k += nkg) {
+                    const int s = ksrc[k];
+                    if (s == -1) continue;
+                    const uint4 u = __ldg(reinterpret_cast<const uint4*>(s >= 0 ? vbase + (size_t)s * Dv : vnew));
+                    const CT* e = reinterpret_cast<const CT*>(&u);
+                    float vf[VEC];
+#pragma unroll
+                    for (int x = 0; x < VEC; ++x) vf[x] = ldf(e, x);
+#pragma unroll
+                    for (int r = 0; r < VR; ++r)
+                        if (r < R) {
+                            const float pw = Ps[r * KS + k];
+#pragma unroll
+                            for (int x = 0; x < VEC; ++x) vacc[r][x] = fmaf(pw, vf[x], vacc[r][x]);
+                        }
+                }
+            }
+        } else {
+    #pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = tid + cc * DEC_THREADS;
+                if (c >= Dv) break;
+    #pragma unroll
+                for (int r = 0; r < RMAX; ++r)
+                    if (r < R) oacc[cc][r] *= s_corr[r];
+                const CT* vbase = vc + (size_t)g * a.L * Dv + c;
+                const CT* vnew = vn + (size_t)g * Dv + c;
+    #pragma unroll 2
+                for (int k = 0; k < KS; k += 4) {
+                    if (k >= nk) break;
+                    float v[4];
+    #pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int s = ksrc[k + i];   // -1 beyond nk as well
+                        v[i] = s >= 0 ? ldf(vbase, (size_t)s * Dv) : (s <= -2 ? ldf(vnew, 0) : 0.f);
+                    }
+    #pragma unroll
+                    for (int r = 0; r < RMAX; ++r)
+                        if (r < R) {
+                            const float4 pw = *reinterpret_cast<const float4*>(Ps + r * KS + k);
+                            oacc[cc][r] = fmaf(pw.x, v[0], oacc[cc][r]);
+                            oacc[cc][r] = fmaf(pw.y, v[1], oacc[cc][r]);
+                            oacc[cc][r] = fmaf(pw.z, v[2], oacc[cc][r]);
+                            oacc[cc][r] = fmaf(pw.w, v[3], oacc[cc][r]);
+                        }
+                }
+            }
+    
+        }
+    }
+    if (vec_values) {   // sum the key groups' partial value sums: red[kg][r][c] -> column c of this thread
+        __syncthreads();
+        float* red = Ps + R * KS + KS;   // behind the key sources
+        if (kg < nkg) {
+#pragma unroll
+            for (int r = 0; r < VR; ++r)
+                if (r < R) {
+#pragma unroll
+                    for (int x = 0; x < VEC; ++x) red[((size_t)kg * R + r) * Dv + cg * VEC + x] = vacc[r][x];
+                }
+        }
+        __syncthreads();
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
             const int c = tid + cc * DEC_THREADS;
             if (c >= Dv) break;
 #pragma unroll
             for (int r = 0; r < RMAX; ++r)
-                if (r < R) oacc[cc][r] *= s_corr[r];
-#pragma unroll 4
-            for (int k = 0; k < nk; ++k) {
-                const float v = Vs[k * Dv + c];
-#pragma unroll
-                for (int r = 0; r < RMAX; ++r)
-                    if (r < R) oacc[cc][r] = fmaf(Ps[r * KS + k], v, oacc[cc][r]);
-            }
+                if (r < R) {
+                    float t = 0.f;
+                    for (int q = 0; q < nkg; ++q) t += red[((size_t)q * R + r) * Dv + c];
+                    oacc[cc][r] = t;
+                }
         }
     }
     const size_t pbase = ((size_t)g * NS + sp) * R;
@@ -650,8 +759,9 @@ static int dispatch_chunk(const CcSeqAttn* a, cudaStream_t st) {
 template <typename CT, typename YT, int RMAX>
 static int launch_decode_r(const CcSeqAttn* a, cudaStream_t st) {
     const int R = a->H / a->G;
-    const int Dkp = a->Dk + ((2 - (a->Dk & 3)) & 3);
-    const size_t smem = sizeof(float) * ((size_t)R * a->Dk + (size_t)KS * Dkp + (size_t)KS * a->Dv + (size_t)R * KS) + sizeof(int) * KS;
+    const int vecw = 16 / (int)sizeof(CT);
+    const size_t red = (RMAX * vecw <= 64 && a->Dv % vecw == 0 && a->Dv / vecw <= DEC_THREADS) ? (size_t)(DEC_THREADS / (a->Dv / vecw)) * R * a->Dv : 0;
+    const size_t smem = sizeof(float) * ((size_t)R * ((a->Dk + 7) & ~7) + (size_t)R * KS + red) + sizeof(int) * KS;
     auto kern = attn_decode_kernel<CT, YT, RMAX>;
     static size_t configured = 48 * 1024;
     if (smem > configured) {
