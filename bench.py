@@ -809,7 +809,13 @@ def _design_kernels(sz, device, hbm):
         ipd = torch.tensor([P], dtype=torch.int32, device=device)
         ws = cache._sequence_workspace(H, window)
         dargs = (q[:1], k[:1], v[:1], cache.k_cache, cache.v_cache, cache.pos, cache.mask, cache.cache_cts, ipd, y[:1], None, window, 2, D ** -0.5)
-        us = _time_events(lambda: seq_ops.seq_attention(*dargs, seq_ops.ATTN_DECODE, ws), 5, 20) * 1e3
+        seq_ops.seq_attention(*dargs, seq_ops.ATTN_DECODE, ws)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()      # 20 launches per replay: the host's per-call cost stays out of the number
+        with torch.cuda.graph(graph):
+            for _ in range(20):
+                seq_ops.seq_attention(*dargs, seq_ops.ATTN_DECODE, ws)
+        us = _time_events(graph.replay, 2, 5) * 1e3 / 20
         live = min(P, window) if window else P
         nbytes = 2 * G * live * D * 2
         out[f"decode_attention_{label}"] = {"us": round(us, 2), "gb_per_s": round(nbytes / us / 1e3, 1),

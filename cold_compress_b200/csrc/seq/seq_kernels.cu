@@ -130,7 +130,8 @@ __device__ __forceinline__ int key_source(const CcSeqAttn& a, int j, int p0) {
 }
 
 // Stages `rows` rows of `width` elements (global, row r at src(r), or zeros when src(r) == nullptr) into fp32 shared
-// memory rows of `stride` floats.  16-byte loads when the rows allow it, element loads otherwise.
+// memory rows of `stride` floats (a multiple of 4, dst 16-byte aligned).  16-byte loads and stores when the rows allow
+// it, element loads otherwise.
 template <typename CT, typename SrcFn>
 __device__ __forceinline__ void stage_rows(float* dst, int stride, int rows, int width, SrcFn src, int tid, int nthreads) {
     constexpr int VEC = 16 / (int)sizeof(CT);
@@ -156,8 +157,10 @@ __device__ __forceinline__ void stage_rows(float* dst, int stride, int rows, int
             for (int e = 0; e < U; ++e) {
                 if (off[e] < 0) continue;
                 const CT* e8 = reinterpret_cast<const CT*>(&u[e]);
+                float4* d4 = reinterpret_cast<float4*>(dst + off[e]);   // stride and column are multiples of 4 floats
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) dst[off[e] + i] = ldf(e8, i);
+                for (int i = 0; i < VEC / 4; ++i)
+                    d4[i] = make_float4(ldf(e8, 4 * i), ldf(e8, 4 * i + 1), ldf(e8, 4 * i + 2), ldf(e8, 4 * i + 3));
             }
         }
     } else {
