@@ -146,8 +146,17 @@ class CcSeqAttn(C.Structure):
         ("scale", C.c_float), ("append", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64)]
 
 
+class CcSeqGemv(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("x_dtype", C.c_int32), ("in_norm_w", C.c_void_p), ("W", C.c_void_p), ("w_dtype", C.c_int32),
+                ("bias", C.c_void_p), ("res", C.c_void_p), ("res_norm_w", C.c_void_p), ("alpha", C.c_float), ("eps", C.c_float),
+                ("limit", C.c_float), ("slope", C.c_float), ("mode", C.c_int32), ("out", C.c_void_p), ("out_dtype", C.c_int32),
+                ("N", C.c_int32), ("K", C.c_int32)]
+
+
+GEMV_PLAIN, GEMV_RESIDUAL, GEMV_GLU = 0, 1, 2
 _i32, _f32, _vp = C.c_int32, C.c_float, C.c_void_p
 SEQ_EXPORTS = {
+    "cc_seq_gemv": (C.c_int, [C.POINTER(CcSeqGemv), C.c_void_p]),
     "cc_seq_abi_version": (C.c_int, []),
     "cc_seq_last_error": (C.c_char_p, []),
     "cc_seq_embed": (C.c_int, [_vp] * 8 + [_i32, _i32, _f32, _i32, _i32, _i32, _i32, _i32, _vp]),

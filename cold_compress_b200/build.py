@@ -4,7 +4,7 @@
 
 `core` = libcc_b200.so (csrc/*.cu: the compressed-KV decode path), `seq` = libcc_b200_seq.so (csrc/seq/*.cu: the
 position-addressed sequence kernels).  Each library is built on its own, so a model that needs one of them does not
-wait for the other.  The built .so files are git-ignored but travel to the GPU box with the gpurun snapshot.
+wait for the other.  The built .so files are git-ignored (the history stays source-only).
 """
 from __future__ import annotations
 

@@ -721,6 +721,119 @@ __global__ void clamped_glu_kernel(const IT* __restrict__ gu, OT* __restrict__ o
     }
 }
 
+// ------------------------------------------------------------------------------------------------ one-token products
+constexpr int GEMV_THREADS = 256, GEMV_ROWS = 16;   // 8 warps x 2 rows per CTA
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    if (threadIdx.x < 32) {
+        t = warp_sum(t);
+        if (threadIdx.x == 0) red[0] = t;
+    }
+    __syncthreads();
+    t = red[0];
+    __syncthreads();
+    return t;
+}
+
+__device__ __forceinline__ float round_like(float v, const float*) { return v; }
+__device__ __forceinline__ float round_like(float v, const __nv_bfloat16*) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// One row of W against the staged input: 16-byte loads, four in flight per lane.
+template <typename WT>
+__device__ __forceinline__ float row_dot(const WT* __restrict__ w, const float* __restrict__ xs, int K, int lane) {
+    constexpr int VEC = 16 / (int)sizeof(WT);
+    float acc = 0.f;
+    if (K % VEC == 0) {
+        const uint4* w16 = reinterpret_cast<const uint4*>(w);
+        const int nv = K / VEC;
+#pragma unroll 4
+        for (int i = lane; i < nv; i += 32) {
+            const uint4 u = __ldg(w16 + i);
+            const WT* e = reinterpret_cast<const WT*>(&u);
+            const float4* x4 = reinterpret_cast<const float4*>(xs + i * VEC);
+#pragma unroll
+            for (int q = 0; q < VEC / 4; ++q) {
+                const float4 xv = x4[q];
+                acc = fmaf(ldf(e, 4 * q + 0), xv.x, acc);
+                acc = fmaf(ldf(e, 4 * q + 1), xv.y, acc);
+                acc = fmaf(ldf(e, 4 * q + 2), xv.z, acc);
+                acc = fmaf(ldf(e, 4 * q + 3), xv.w, acc);
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(ldf(w, k), xs[k], acc);
+    }
+    return warp_sum(acc);
+}
+
+template <typename WT, typename XT, typename OT>
+__global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const CcSeqGemv g) {
+    extern __shared__ float4 smg4[];
+    float* xs = reinterpret_cast<float*>(smg4);   // [K] the product's input, rounded as the weights are
+    __shared__ float red[32];
+    const int K = g.K, N = g.N, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const XT* x = (const XT*)g.x;
+    const WT* W = (const WT*)g.W;
+    float rin = 1.f;
+    if (g.in_norm_w != nullptr) {
+        float ss = 0.f;
+        for (int k = tid; k < K; k += GEMV_THREADS) { const float v = ldf(x, k); ss += v * v; }
+        rin = 1.0f / sqrtf(block_sum(ss, red) / (float)K + g.eps);
+    }
+    for (int k = tid; k < K; k += GEMV_THREADS) {
+        float v = ldf(x, k);
+        if (g.in_norm_w != nullptr) v = v * rin * (1.0f + g.in_norm_w[k]);
+        xs[k] = round_like(v, W);
+    }
+    float rres = 1.f;
+    if (g.mode == CC_GEMV_RESIDUAL && g.res_norm_w != nullptr) {
+        float ss = 0.f;
+        for (int n = tid; n < N; n += GEMV_THREADS) { const float v = g.res[n]; ss += v * v; }
+        rres = 1.0f / sqrtf(block_sum(ss, red) / (float)N + g.eps);
+    }
+    __syncthreads();
+    for (int i = 0; i < GEMV_ROWS / (GEMV_THREADS / 32); ++i) {
+        const int n = blockIdx.x * GEMV_ROWS + i * (GEMV_THREADS / 32) + warp;
+        if (n >= N) break;
+        float acc = row_dot<WT>(W + (size_t)n * K, xs, K, lane);
+        if (g.mode == CC_GEMV_GLU) {
+            const float up = row_dot<WT>(W + (size_t)(N + n) * K, xs, K, lane);
+            if (lane == 0) {
+                const float gt = fminf(acc, g.limit);
+                const float u = fminf(fmaxf(up, -g.limit), g.limit);
+                stf((OT*)g.out, n, gt * (1.0f / (1.0f + expf(-g.slope * gt))) * (u + 1.0f));
+            }
+            continue;
+        }
+        if (lane != 0) continue;
+        if (g.bias != nullptr) acc += g.bias[n];
+        if (g.mode == CC_GEMV_RESIDUAL) {
+            float r = g.res[n];
+            if (g.res_norm_w != nullptr) r = r * rres * (1.0f + g.res_norm_w[n]);
+            acc = g.alpha * r + acc;
+        }
+        stf((OT*)g.out, n, acc);
+    }
+}
+
+template <typename WT, typename XT, typename OT>
+static int launch_gemv(const CcSeqGemv* g, cudaStream_t st) {
+    const size_t smem = sizeof(float) * (size_t)((g->K + 3) & ~3);
+    auto kern = gemv_kernel<WT, XT, OT>;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        configured = smem;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(CC_SEQ_ERR_CUDA, cudaGetErrorString(e));
+    }
+    kern<<<(g->N + GEMV_ROWS - 1) / GEMV_ROWS, GEMV_THREADS, smem, st>>>(*g);
+    return cuda_check("gemv_kernel");
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 static int check_attn(const CcSeqAttn* a) {
     if (!a || !a->q || !a->k_new || !a->v_new || !a->k_cache || !a->v_cache || !a->pos || !a->input_pos || !a->y)
@@ -897,6 +1010,23 @@ int cc_seq_clamped_glu(const void* gu, void* out, int32_t io_dtype, int32_t out_
      cuda_check("clamped_glu_kernel"))
     CCS_DISPATCH2(io_dtype, out_dtype, CALL);
 #undef CALL
+}
+
+int cc_seq_gemv(const CcSeqGemv* g, void* stream) {
+    if (!g || !g->x || !g->W || !g->out || g->N < 1 || g->K < 1 || (g->mode == CC_GEMV_RESIDUAL && !g->res) ||
+        g->mode < CC_GEMV_PLAIN || g->mode > CC_GEMV_GLU)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "gemv: bad argument");
+    if (g->in_norm_w && g->x_dtype != CC_DT_F32) return fail(CC_SEQ_ERR_INVALID_ARG, "gemv: a normed input is an fp32 sum");
+    if (g->mode != CC_GEMV_GLU && g->out_dtype != CC_DT_F32) return fail(CC_SEQ_ERR_INVALID_ARG, "gemv: fp32 output expected");
+    if ((size_t)g->K * 4 > 200 * 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "gemv: input longer than 51200");
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool wb = g->w_dtype == CC_DT_BF16, xb = g->x_dtype == CC_DT_BF16, ob = g->out_dtype == CC_DT_BF16;
+    if (wb && xb && ob) return launch_gemv<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(g, st);
+    if (wb && xb && !ob) return launch_gemv<__nv_bfloat16, __nv_bfloat16, float>(g, st);
+    if (wb && !xb && ob) return launch_gemv<__nv_bfloat16, float, __nv_bfloat16>(g, st);
+    if (wb && !xb && !ob) return launch_gemv<__nv_bfloat16, float, float>(g, st);
+    if (!wb && !xb && !ob) return launch_gemv<float, float, float>(g, st);
+    return fail(CC_SEQ_ERR_INVALID_ARG, "gemv: unsupported combination of element types");
 }
 
 }  // extern "C"

@@ -27,6 +27,8 @@ _library.define("seq_attention(Tensor q, Tensor k_new, Tensor v_new, Tensor(a!) 
                 "int sink_mode, float scale, int mode, Tensor(g!)? workspace) -> ()")
 _library.define("seq_residual_norm(Tensor(a!) x, Tensor? y, Tensor w, float alpha, float eps, Tensor(b!)? x_act) -> ()")
 _library.define("seq_clamped_glu(Tensor gu, Tensor(a!) out, float limit, float slope) -> ()")
+_library.define("seq_gemv(Tensor x, Tensor? in_norm_w, Tensor w, Tensor? bias, Tensor? res, Tensor? res_norm_w, Tensor(a!) out, "
+                "int mode, float alpha, float eps, float limit, float slope) -> ()")
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -133,12 +135,27 @@ def _seq_clamped_glu(gu, out, limit, slope):
                                                       _stream()), "cc_seq_clamped_glu")
 
 
+def _seq_gemv(x, in_norm_w, w, bias, res, res_norm_w, out, mode, alpha, eps, limit, slope):
+    """One-token product with the post-sum norm folded into its prologue / epilogue (cc_seq_gemv)."""
+    _need(("x", x, None), ("in_norm_w", in_norm_w, torch.float32), ("w", w, None), ("bias", bias, torch.float32),
+          ("res", res, torch.float32), ("res_norm_w", res_norm_w, torch.float32), ("out", out, None))
+    g = _lib.CcSeqGemv()
+    rows, K = w.shape
+    N = rows // 2 if mode == _lib.GEMV_GLU else rows
+    assert x.numel() == K and out.numel() == N and (res is None or res.numel() == N) and (in_norm_w is None or in_norm_w.numel() == K)
+    g.x, g.x_dtype, g.in_norm_w, g.W, g.w_dtype = _p(x), _dt(x), _p(in_norm_w), _p(w), _dt(w)
+    g.bias, g.res, g.res_norm_w = _p(bias), _p(res), _p(res_norm_w)
+    g.alpha, g.eps, g.limit, g.slope, g.mode = float(alpha), float(eps), float(limit), float(slope), int(mode)
+    g.out, g.out_dtype, g.N, g.K = _p(out), _dt(out), N, K
+    _lib.check_seq(_lib.load_seq().cc_seq_gemv(C.byref(g), _stream()), "cc_seq_gemv")
+
+
 def _no_cpu(*_a, **_k):
     raise _lib.CcError("cold_compress_b200 sequence ops have no CPU implementation (sm_100a only)")
 
 
 for _name, _fn in (("seq_embed", _seq_embed), ("seq_qkv_prepare", _seq_qkv_prepare), ("seq_attention", _seq_attention),
-                   ("seq_residual_norm", _seq_residual_norm), ("seq_clamped_glu", _seq_clamped_glu)):
+                   ("seq_residual_norm", _seq_residual_norm), ("seq_clamped_glu", _seq_clamped_glu), ("seq_gemv", _seq_gemv)):
     _library.impl(_name, _fn, "CUDA")
     _library.impl(_name, _no_cpu, "CPU")
 
@@ -147,3 +164,4 @@ seq_qkv_prepare = torch.ops.cold_compress_b200.seq_qkv_prepare
 seq_attention = torch.ops.cold_compress_b200.seq_attention
 seq_residual_norm = torch.ops.cold_compress_b200.seq_residual_norm
 seq_clamped_glu = torch.ops.cold_compress_b200.seq_clamped_glu
+seq_gemv = torch.ops.cold_compress_b200.seq_gemv

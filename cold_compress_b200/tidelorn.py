@@ -204,6 +204,9 @@ class TidelornTransformer(nn.Module):
         if len(widths) > 1:
             raise ValueError("layers that mix values must agree on kv_heads * vdim")
         self._first_mixing = mixing[0] if mixing else None
+        # one-token steps through the fused product kernels (norm folded into the products); False = the same
+        # kernels as a prompt portion of one token (library products + norm launches), used by the A/B tests
+        self.fused_decode = True
 
     # ---- caches ---------------------------------------------------------------------------------
     def layer_cache_plan(self, cache_kwargs: Dict[str, Any], max_seq_length: int) -> Dict[str, Any]:
@@ -271,6 +274,8 @@ class TidelornTransformer(nn.Module):
         ip = input_pos.reshape(-1)[:1]
         ip = ip if ip.dtype == torch.int32 else ip.to(torch.int32)
         T, E, dev = tokens.numel(), self.config.dim, tokens.device
+        if T == 1 and not is_prefill and self.fused_decode and collect is None:
+            return self._decode_fused(tokens, ip)
         x = torch.empty(T, E, dtype=torch.float32, device=dev)
         x_act = x if self.dtype == torch.float32 else torch.empty(T, E, dtype=self.dtype, device=dev)
         side = None if x_act is x else x_act
@@ -294,10 +299,57 @@ class TidelornTransformer(nn.Module):
         self.norm(xs, None, None if xs_act is xs else xs_act)
         return _mm(xs_act, self.output).view(1, xs.shape[0], -1)
 
+    def _decode_fused(self, tokens: Tensor, ip: Tensor) -> Tensor:
+        """One token with the stream kept as the pre-norm sum `s` of the last sublayer: every product reads
+        `norm(s)` through its prologue and the row-parallel ones write `alpha * norm(s) + W y` through their epilogue
+        (cc_seq_gemv), so no norm launch separates two products.  Per layer: qkv product, q/k/v preparation, attention +
+        append, o product, gate/up product with the clamped unit, down product."""
+        E, dev, dt = self.config.dim, tokens.device, self.dtype
+        f32 = dict(dtype=torch.float32, device=dev)
+        x0 = torch.empty(1, E, **f32)
+        x0_act = x0 if dt == torch.float32 else torch.empty(1, E, dtype=dt, device=dev)
+        self.tok_embeddings(tokens, ip, x0, None if x0_act is x0 else x0_act)
+        cur, cur_w, cur_in = x0, None, x0_act     # the stream (a sum, or the embedding), its norm gain, what products read
+        v_first = None
+        gemv = seq_ops.seq_gemv
+        for block in self.layers:
+            att = block.attention
+            H, G, Dk, Dv = att.heads, att.kv_heads, att.head_dim, att.v_head_dim
+            qkv = torch.empty(1, att.wqkv.shape[0], **f32)
+            gemv(cur_in, cur_w, att.wqkv, None, None, None, qkv, _lib.GEMV_PLAIN, 1.0, att.eps, 0.0, 0.0)
+            q = torch.empty(1, H, Dk, **f32)
+            k = torch.empty(1, G, Dk, dtype=dt, device=dev)
+            v = torch.empty(1, G, Dv, dtype=dt, device=dev)
+            mix_from = v_first if att.v_mix else None
+            seq_ops.seq_qkv_prepare(qkv, att.bqkv, ip, att.vmix if mix_from is not None else None, mix_from, q, k, v,
+                                    H, G, Dk, Dv, att.eps, att.unit_norm, att.gain_coef, att.gain_every)
+            if att is self._first_mixing:
+                v_first = v
+            y = torch.empty(1, H, Dv, dtype=dt, device=dev)
+            att.kv_cache.sequence_step(q, k, v, ip, y, window=att.window, sink=att.sink, sink_mode=att.sink_mode, scale=att.scale)
+            s1 = torch.empty(1, E, **f32)
+            gemv(y, None, att.wo, None, cur, cur_w, s1, _lib.GEMV_RESIDUAL, block.norm1.alpha, block.norm1.eps, 0.0, 0.0)
+            cur, cur_w, cur_in = s1, block.norm1.weight, s1
+            ff = block.feed_forward
+            if ff is not None:
+                act = torch.empty(1, ff.ff, dtype=dt, device=dev)
+                gemv(s1, block.norm1.weight, ff.w13, None, None, None, act, _lib.GEMV_GLU, 1.0, block.norm1.eps, ff.limit, ff.slope)
+                s2 = torch.empty(1, E, **f32)
+                gemv(act, None, ff.w2, None, s1, block.norm1.weight, s2, _lib.GEMV_RESIDUAL, block.norm2.alpha, block.norm2.eps, 0.0, 0.0)
+                cur, cur_w, cur_in = s2, block.norm2.weight, s2
+        xs = cur.clone()
+        if cur_w is not None:
+            seq_ops.seq_residual_norm(xs, None, cur_w, 1.0, self.norm.eps, None)
+        logits = torch.empty(1, self.config.vocab_size, **f32)
+        gemv(xs, self.norm.weight, self.output, None, None, None, logits, _lib.GEMV_PLAIN, 1.0, self.norm.eps, 0.0, 0.0)
+        return logits.view(1, 1, -1)
+
     def kernels_per_token(self) -> int:
-        """Launches of this package's kernels in one decode step: embedding, per layer [prepare, attention+append,
-        norm, (gate, norm)], final norm."""
-        return 2 + sum(3 + (2 if b.feed_forward is not None else 0) for b in self.layers)
+        """Launches of this package's kernels in one decode step: embedding, per layer [qkv product, preparation,
+        attention + append, o product, (gate/up product, down product)], last norm, output product."""
+        if not self.fused_decode:
+            return 2 + sum(3 + (2 if b.feed_forward is not None else 0) for b in self.layers)
+        return 3 + sum(4 + (2 if b.feed_forward is not None else 0) for b in self.layers)
 
     # ---- weights --------------------------------------------------------------------------------
     def load_tensors(self, tensors: Dict[str, Tensor]):

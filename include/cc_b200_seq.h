@@ -103,6 +103,37 @@ int cc_seq_residual_norm(float* x, const void* y, int32_t y_dtype, const float* 
 int cc_seq_clamped_glu(const void* gu, void* out, int32_t io_dtype, int32_t out_dtype, float limit, float slope,
                        int32_t T, int32_t F, void* stream);
 
+/*
+ * One-token matrix-vector product out = epilogue(W xin) for the decode step, with the post-sum norm folded in:
+ *   xin[k] = x[k]                                    (in_norm_w == NULL; x in x_dtype)
+ *          = x[k] * rinv(x) * (1 + in_norm_w[k])      (x fp32 = a pre-norm sum; rinv = 1/sqrt(mean(x^2) + eps)),
+ *            rounded to the weights' type, as the prompt path rounds its product inputs
+ * epilogues (acc = W xin + bias in fp32):
+ *   CC_GEMV_PLAIN     out[n] = acc                                             (fp32)
+ *   CC_GEMV_RESIDUAL  out[n] = alpha * r[n] + acc, r = res or res * rinv(res) * (1 + res_norm_w)   (fp32 pre-norm sum)
+ *   CC_GEMV_GLU       rows n and N + n of W: g = min(acc_n, limit), u = clamp(acc_{N+n}, +-limit),
+ *                     out[n] = g * sigmoid(slope * g) * (u + 1)                 (out_dtype)
+ * Every CTA recomputes the row statistics it needs (K and N floats from L2) instead of waiting for a norm kernel.
+ */
+#define CC_GEMV_PLAIN     0
+#define CC_GEMV_RESIDUAL  1
+#define CC_GEMV_GLU       2
+
+typedef struct CcSeqGemv {
+    const void* x;  int32_t x_dtype;
+    const float* in_norm_w;
+    const void* W;  int32_t w_dtype;      /* [N (2N for GLU), K] row-major */
+    const float* bias;                    /* [N] or NULL (not with GLU) */
+    const float* res;                     /* [N] fp32, RESIDUAL only */
+    const float* res_norm_w;              /* [N] or NULL */
+    float alpha, eps, limit, slope;
+    int32_t mode;
+    void* out;      int32_t out_dtype;
+    int32_t N, K;
+} CcSeqGemv;
+
+int cc_seq_gemv(const CcSeqGemv* g, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -298,6 +298,51 @@ def test_prompt_portions_and_decoding_agree_with_the_whole(dtype, portions):
     assert row_error(got, want).max() < _tol(dtype, cfg, W, tokens, want), row_error(got, want).max()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_one_token_products_equal_the_unfused_step(dtype):
+    """The decode step with the norm folded into hand-written products against the same step through library products
+    and norm launches: same numbers up to summation order."""
+    cfg = make_config(default_layers())
+    W = random_weights(cfg, seed=21)
+    tokens = torch.randint(0, cfg["vocab"], (40,), generator=torch.Generator().manual_seed(22)).tolist()
+    outs = []
+    for fused in (True, False):
+        model = build_model(cfg, W, dtype, 40)
+        model.fused_decode = fused
+        assert model.kernels_per_token() == (3 + 4 * 7 + 2 * 6 if fused else 2 + 3 * 7 + 2 * 6)
+        outs.append(_run_portions(model, tokens, (20,) + (1,) * 20))
+    want = _reference_logits(cfg, W, tokens)
+    assert row_error(outs[0], outs[1]).max() < (2e-5 if dtype == torch.float32 else 3e-2)
+    assert row_error(outs[0], want).max() < _tol(dtype, cfg, W, tokens, want)
+
+
+def test_one_token_product_kernel_alone():
+    ops = _ops()
+    from cold_compress_b200 import _lib
+    g = torch.Generator().manual_seed(23)
+    N, K, F = 37, 70, 29
+    x, w, b = torch.randn(K, generator=g), torch.randn(N, K, generator=g) * 0.2, torch.randn(N, generator=g)
+    nw, res, rw = torch.randn(K, generator=g) * 0.3, torch.randn(N, generator=g), torch.randn(N, generator=g) * 0.3
+    xn = R.zero_centred_norm(x.double(), nw.double(), 1e-3)
+    out = torch.empty(N, device=DEV)
+    ops.seq_gemv(x.to(DEV), nw.to(DEV), w.to(DEV), b.to(DEV), None, None, out, _lib.GEMV_PLAIN, 1.0, 1e-3, 0.0, 0.0)
+    assert (out.cpu().double() - (w.double() @ xn + b.double())).abs().max() < 1e-5
+    ops.seq_gemv(x.to(DEV), None, w.to(DEV), None, res.to(DEV), rw.to(DEV), out, _lib.GEMV_RESIDUAL, 1.75, 1e-3, 0.0, 0.0)
+    want = 1.75 * R.zero_centred_norm(res.double(), rw.double(), 1e-3) + w.double() @ x.double()
+    assert (out.cpu().double() - want).abs().max() < 1e-5
+    w2 = torch.randn(2 * F, K, generator=g)
+    act = torch.empty(F, device=DEV)
+    ops.seq_gemv(x.to(DEV), None, w2.to(DEV), None, None, None, act, _lib.GEMV_GLU, 1.0, 1e-3, 0.6, 1.702)
+    gu = (w2.double() @ x.double())
+    gate, up = gu[:F].clamp(max=0.6), gu[F:].clamp(-0.6, 0.6)
+    assert (act.cpu().double() - gate * torch.sigmoid(1.702 * gate) * (up + 1)).abs().max() < 1e-5
+    # bf16 weights and input, 16-byte rows
+    K2 = 64
+    xb, wb = torch.randn(K2, generator=g).to(torch.bfloat16), (torch.randn(N, K2, generator=g) * 0.2).to(torch.bfloat16)
+    ops.seq_gemv(xb.to(DEV), None, wb.to(DEV), None, None, None, out, _lib.GEMV_PLAIN, 1.0, 1e-3, 0.0, 0.0)
+    assert (out.cpu().double() - wb.double() @ xb.double()).abs().max() < 1e-5
+
+
 def test_sequences_one_after_another_reuse_the_slots():
     """Three sequences of unequal length through one model, the caches given back in between: each equals itself
     alone.  The second is longer than the first, the third shorter, so rings and full caches are both re-filled and
