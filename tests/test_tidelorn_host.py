@@ -140,3 +140,23 @@ def test_restatement_is_causal_and_windows_forget():
     la, lb = R.forward(a, W, cfg), R.forward(b, W, cfg)
     assert not torch.allclose(la[6], lb[6])
     assert torch.allclose(R.forward(a[:5], W, cfg), la[:5])
+
+
+def test_sequence_library_exports_every_declared_symbol():
+    """Every function include/cc_b200_seq.h declares is bound in _lib.SEQ_EXPORTS and exported by the built library."""
+    import re
+    from pathlib import Path
+    from cold_compress_b200 import _lib
+    from cold_compress_b200.build import build_seq_extension
+    header = (Path(__file__).resolve().parent.parent / "include" / "cc_b200_seq.h").read_text()
+    declared = set(re.findall(r"\b(cc_seq_\w+)\s*\(", header))
+    assert declared == set(_lib.SEQ_EXPORTS), declared ^ set(_lib.SEQ_EXPORTS)
+    build_seq_extension()
+    lib = _lib.load_seq()
+    assert lib.cc_seq_abi_version() == _lib.SEQ_ABI_VERSION
+    assert lib.cc_seq_decode_workspace(8, 2, 64, 1000, 0) > 0
+    # argument checks come back as error codes with a message, not as faults
+    a = _lib.CcSeqAttn()
+    assert lib.cc_seq_attention(a, None) < 0 and b"NULL" in lib.cc_seq_last_error()
+    g = _lib.CcSeqGemv()
+    assert lib.cc_seq_gemv(g, None) < 0 and b"gemv" in lib.cc_seq_last_error()
