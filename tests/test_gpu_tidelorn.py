@@ -428,3 +428,47 @@ def test_checkpoint_folder_generate_and_graphed_decoder(tmp_path):
                 break
         assert stats["decode_tokens"] == new
         reset_caches(model)
+
+
+def test_trace_replay_command(tmp_path):
+    """bin/trace_run as a user runs it: a checkpoint folder, steps on standard input (a whole prompt, a prompt in
+    portions with the last tokens alone, a second sequence after the first has ended), logits files and `done` lines."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    import numpy as np
+    from cold_compress_b200.checkpoint import write_safetensors
+    root = Path(__file__).resolve().parent.parent
+    cfg = make_config([global_layer(heads=6, kv_heads=3, dim=16, vdim=24, every=9), window_layer(13, heads=3, kv_heads=3, dim=24, vdim=24),
+                       global_layer(heads=6, kv_heads=3, dim=16, vdim=24, ff=0), window_layer(50, heads=6, kv_heads=1, dim=8, vdim=72)],
+                      width=88, vocab=301, alpha=3.0, bigram=(211, 13, 17))
+    W = random_weights(cfg, seed=31)
+    model_dir = tmp_path / "ckpt"
+    model_dir.mkdir()
+    (model_dir / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(model_dir / "model.safetensors", W)
+    g = torch.Generator().manual_seed(32)
+    a = torch.randint(0, 301, (75,), generator=g).tolist()
+    b = torch.randint(0, 301, (41,), generator=g).tolist()
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[30:32], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[32:73], "want": [5, 40]}], "end": []},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[73:74], "want": [0]}], "end": []},
+             {"step": 4, "entries": [{"id": "a", "tokens": a[74:75], "want": [0]}], "end": ["a"]},
+             {"step": 5, "entries": [{"id": "b", "tokens": b, "want": [0, 20, 40]}], "end": ["b"]}]
+    want = {0: [0, 29], 2: [37, 72], 3: [73], 4: [74]}
+    la, lb = _reference_logits(cfg, W, a), _reference_logits(cfg, W, b)
+    for dtype, tol in (("float32", 2e-4), ("bfloat16", BF16_TOL)):
+        out = tmp_path / ("out_" + dtype)
+        r = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype,
+                            "--out", str(out), "--max-tokens", "75"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                           capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert [ln for ln in r.stdout.splitlines() if ln.startswith("done")] == [f"done {i}" for i in range(6)]
+        assert not (out / "1.f32").exists()
+        for step, rows in want.items():
+            got = torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(len(rows), -1).copy())
+            assert row_error(got, la[rows]).max() < tol, (dtype, step)
+        got = torch.from_numpy(np.fromfile(out / "5.f32", dtype="<f4").reshape(3, -1).copy())
+        assert row_error(got, lb[[0, 20, 40]]).max() < tol
