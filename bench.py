@@ -673,10 +673,10 @@ def _tidelorn_model(sz, device, dtype):
     layers = []
     for i in range(sz["layers"]):
         kind = "attention" if i % 2 == 0 else "attention_2"
-        extra = {"q_temp": {"coef": 0.3, "every": 256}} if kind == "attention" else {"mask": {"size": sz["window"]}}
+        extra = {"q_temp": {"coef": 0.25, "every": 128}} if kind == "attention" else {"mask": {"size": sz["window"]}}
         layers.append({"type": kind, "mixer": dict(mixer, **extra), "mlp": {"kind": "dense", "ff": sz["ff"], "limit": 7.0}})
-    cfg = {"architecture": "Tidelorn", "vocab": sz["vocab"], "width": sz["width"], "postln_alpha": 2.0, "norm": {"eps": 1e-6},
-           "embedding": {"scale": sz["width"] ** 0.5, "bigram": {"buckets": 100003, "mul_prev": 31, "mul_cur": 7}}, "layers": layers}
+    cfg = {"architecture": "Tidelorn", "vocab": sz["vocab"], "width": sz["width"], "postln_alpha": 2.0, "norm": {"eps": 1e-5},
+           "embedding": {"scale": sz["width"] ** 0.5, "bigram": {"buckets": 100003, "mul_prev": 8191, "mul_cur": 127}}, "layers": layers}
     with torch.device(device):
         model = TidelornTransformer.from_config(cfg, dtype)
     gen = torch.Generator(device=device).manual_seed(0)
