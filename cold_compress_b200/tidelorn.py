@@ -274,7 +274,7 @@ class TidelornTransformer(nn.Module):
         ip = input_pos.reshape(-1)[:1]
         ip = ip if ip.dtype == torch.int32 else ip.to(torch.int32)
         T, E, dev = tokens.numel(), self.config.dim, tokens.device
-        if T == 1 and not is_prefill and self.fused_decode and collect is None:
+        if T == 1 and not is_prefill and self.fused_decode and collect is None and self._fused_decode_fits():
             return self._decode_fused(tokens, ip)
         x = torch.empty(T, E, dtype=torch.float32, device=dev)
         x_act = x if self.dtype == torch.float32 else torch.empty(T, E, dtype=self.dtype, device=dev)
@@ -289,6 +289,8 @@ class TidelornTransformer(nn.Module):
             block.norm1(x, out, side)
             if block.feed_forward is not None:
                 block.norm2(x, block.feed_forward(x_act), side)
+            elif block.norm2 is not None:   # a second norm without a feed-forward: x <- norm2(alpha * x)
+                block.norm2(x, None, side)
             if collect is not None:
                 collect.append(x.clone())
         if logits_at is None:
@@ -298,6 +300,13 @@ class TidelornTransformer(nn.Module):
         xs_act = xs if self.dtype == torch.float32 else torch.empty_like(xs, dtype=self.dtype)
         self.norm(xs, None, None if xs_act is xs else xs_act)
         return _mm(xs_act, self.output).view(1, xs.shape[0], -1)
+
+    def _fused_decode_fits(self) -> bool:
+        """The one-token product kernel stages its input vector in shared memory (up to 51200 elements) and knows the
+        two sublayer forms of a block; anything else takes the general step."""
+        widest = max([self.config.dim] + [b.feed_forward.ff for b in self.layers if b.feed_forward is not None]
+                     + [b.attention.heads * b.attention.v_head_dim for b in self.layers])
+        return widest <= 51200 and all(b.norm2 is None or b.feed_forward is not None for b in self.layers)
 
     def _decode_fused(self, tokens: Tensor, ip: Tensor) -> Tensor:
         """One token with the stream kept as the pre-norm sum `s` of the last sublayer: every product reads
@@ -391,6 +400,10 @@ class TidelornTransformer(nn.Module):
                 f = block.feed_forward
                 put(f.w13, torch.cat([get(p + "mlp.gate", (f.ff, cfg.dim)), get(p + "mlp.up", (f.ff, cfg.dim))]))
                 put(f.w2, get(p + "mlp.down", (cfg.dim, f.ff)))
+                put(block.norm2.weight, get(p + "norm2", (cfg.dim,)).float())
+            elif p + "norm2" in tensors:
+                # the checkpoint carries a second norm for a layer without feed-forward: it is applied to alpha * x
+                block.norm2 = PostSumNorm(cfg.dim, cfg.norm_eps, cfg.postln_alpha).to(block.norm1.weight.device)
                 put(block.norm2.weight, get(p + "norm2", (cfg.dim,)).float())
         put(self.norm.weight, get("final.norm", (cfg.dim,)).float())
         put(self.output, get("head", (cfg.vocab_size, cfg.dim)))

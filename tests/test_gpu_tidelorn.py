@@ -394,6 +394,23 @@ def test_other_sizes(layers, kw, dtype):
     assert row_error(got, want).max() < _tol(dtype, cfg, W, tokens, want), row_error(got, want).max()
 
 
+def test_second_norm_without_feed_forward():
+    """A checkpoint that carries norm2 for a layer without feed-forward: the norm is applied to alpha * x, in prompt
+    portions and in single-token steps (which then take the general step, not the fused products)."""
+    cfg = make_config([global_layer(ff=0), window_layer(6), global_layer(ff=0, v_mix=False)], width=40, vocab=61)
+    W = random_weights(cfg, seed=41)
+    g = torch.Generator().manual_seed(42)
+    W["l0.norm2"] = (torch.randn(40, generator=g) * 0.2).to(torch.bfloat16)
+    tokens = torch.randint(0, 61, (24,), generator=g).tolist()
+    want = _reference_logits(cfg, W, tokens)
+    model = build_model(cfg, W, torch.float32, 24)
+    assert model.layers[0].norm2 is not None and model.layers[2].norm2 is None and not model._fused_decode_fits()
+    got = _run_portions(model, tokens, (10, 1, 1, 12))
+    assert row_error(got, want).max() < fp32_tolerance(cfg, W, tokens, want)
+    W.pop("l0.norm2")
+    assert row_error(_reference_logits(cfg, W, tokens), want).max() > 1e-3   # the extra norm matters
+
+
 def test_checkpoint_folder_generate_and_graphed_decoder(tmp_path):
     """From a checkpoint folder through load_model, setup_caches and generate(): greedy tokens equal the restatement's
     arg-max continuation, with the prompt whole or in portions, eager or graph-captured."""

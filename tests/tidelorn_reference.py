@@ -21,10 +21,6 @@ def zero_centred_norm(x, w, eps):
     return rms_unit(x, eps) * (1.0 + w)
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def sinusoid(positions, width, dtype):
     """[T, E]: even entries sin(p * w_i), odd entries cos(p * w_i), w_i = 10000^(-2i/E)."""
     i = torch.arange(0, width, 2, dtype=dtype)
@@ -122,6 +118,8 @@ def forward(tokens, W, cfg, collect=None):
         x = zero_centred_norm(alpha * x + out, W[pfx + "norm1"], eps)
         if layer.get("mlp"):
             x = zero_centred_norm(alpha * x + clamped_glu(x, W, pfx + "mlp.", layer["mlp"]), W[pfx + "norm2"], eps)
+        elif pfx + "norm2" in W:   # a checkpoint that carries a second norm for a layer without feed-forward
+            x = zero_centred_norm(alpha * x, W[pfx + "norm2"], eps)
         if collect is not None:
             collect.append(x.clone())
     return zero_centred_norm(x, W["final.norm"], eps) @ W["head"].T
