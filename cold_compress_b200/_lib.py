@@ -134,7 +134,7 @@ def check(rc: int, what: str = "") -> int:
 
 # --------------------------------------------------------------------------- libcc_b200_seq.so (include/cc_b200_seq.h)
 SEQ_SO_PATH = Path(os.environ.get("CC_B200_SEQ_LIB", PKG / "libcc_b200_seq.so"))
-SEQ_ABI_VERSION = 1
+SEQ_ABI_VERSION = 2
 DT_F32, DT_BF16 = 0, 1
 SINK_NONE, SINK_LEARNED, SINK_ZERO = 0, 1, 2
 
@@ -169,6 +169,57 @@ SEQ_EXPORTS = {
     "cc_seq_residual_norm": (C.c_int, [_vp, _vp, _i32, _vp, _f32, _f32, _vp, _i32, _i32, _i32, _vp]),
     "cc_seq_clamped_glu": (C.c_int, [_vp, _vp, _i32, _i32, _f32, _f32, _i32, _i32, _vp]),
 }
+
+# ---- second part of the header: state-carrying layers (csrc/seq/mix_kernels.cu)
+ACT_NONE, ACT_GELU_TANH, ACT_SILU, ACT_TANH, ACT_SIGMOID = range(5)
+_i64 = C.c_int64
+
+
+class CcSeqGatedNorm(C.Structure):
+    _fields_ = [("x", _vp), ("a", _vp), ("lda", _i64), ("ga", _vp), ("ldga", _i64), ("ba", _vp),
+                ("b", _vp), ("ldb", _i64), ("gb", _vp), ("ldgb", _i64), ("bb", _vp), ("w", _vp),
+                ("h", _vp), ("h_act", _vp), ("act_dtype", _i32), ("rows", _vp), ("T", _i32), ("E", _i32), ("groups", _i32),
+                ("eps", _f32)]
+
+
+class CcSeqLatentPrep(C.Structure):
+    _fields_ = [("inp", _vp), ("ld", _i64)] + [(n, _i32) for n in ("off_q", "q_rank", "off_kv", "kv_rank", "rot_dim", "rot_dims")] + [
+        (n, _vp) for n in ("wq", "wkv", "inv_freq", "input_pos", "cq", "krow", "vrow")] + [("dtype", _i32), ("T", _i32), ("eps", _f32)]
+
+
+class CcSeqLatentExpand(C.Structure):
+    _fields_ = [("kv_old", _vp), ("kv_new", _vp), ("ld_kv", _i64), ("lat_old", _vp), ("lat_new", _vp), ("ld_lat", _i64)] + [
+        (n, _vp) for n in ("k_old", "v_old", "k_new", "v_new")] + [
+        (n, _i32) for n in ("dtype", "n_old", "n_new", "H", "D", "V", "R", "kv_rank")]
+
+
+class CcSeqWkv(C.Structure):
+    _fields_ = [(n, _vp) for n in ("r", "k", "v", "wraw", "w0", "u", "state", "o")] + [(n, _i32) for n in ("T", "H", "D")]
+
+
+class CcSeqMoeCombine(C.Structure):
+    _fields_ = [(n, _vp) for n in ("ids", "wts", "slot", "y", "h", "shared", "sg")] + [("ld_sg", _i64), ("out", _vp)] + [
+        (n, _i32) for n in ("T", "E", "top", "n_real")]
+
+
+SEQ_EXPORTS.update({
+    "cc_seq_embed_rows": (C.c_int, [_vp, _vp, _i32, _vp, _i32, _i32, _f32, _vp]),
+    "cc_seq_gated_group_norm": (C.c_int, [C.POINTER(CcSeqGatedNorm), _vp]),
+    "cc_seq_token_shift": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _vp]),
+    "cc_seq_gated_unit": (C.c_int, [_vp, _i64, _i32, _i32, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "cc_seq_latent_prepare": (C.c_int, [C.POINTER(CcSeqLatentPrep), _vp]),
+    "cc_seq_rope_heads": (C.c_int, [_vp, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _i32, _vp]),
+    "cc_seq_latent_expand": (C.c_int, [C.POINTER(CcSeqLatentExpand), _vp]),
+    "cc_seq_head_gate": (C.c_int, [_vp, _i32, _vp, _i64, _i32, _i32, _i32, _vp]),
+    "cc_seq_head_gemv": (C.c_int, [_vp, _i32, _vp, _i32, _i64, _vp, _i32, _i64, _vp, _i32, _i32, _i32, _vp]),
+    "cc_seq_wkv": (C.c_int, [C.POINTER(CcSeqWkv), _vp]),
+    "cc_seq_head_norm_gate": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _vp]),
+    "cc_seq_moe_route": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "cc_seq_moe_group": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
+    "cc_seq_gather_rows": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "cc_seq_moe_expert_tokens": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "cc_seq_moe_combine": (C.c_int, [C.POINTER(CcSeqMoeCombine), _vp]),
+})
 
 _seq_lib = None
 

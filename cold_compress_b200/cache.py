@@ -771,9 +771,56 @@ class KVCacheAnalysis(KVCacheFull):
         return stats
 
 
+class KVCacheLatent(KVCacheFull):
+    """The cache of a latent (low-rank) attention layer: one row per position, shared by all query heads, holding the
+    normalised key/value latent followed by the rotated key part (`k_cache` [1, 1, L, rank + rot]); `v_cache`
+    [1, 1, L, rank] holds the latent again as the value row of the absorbed one-token step.  Nothing is ever evicted
+    (slot = position), so it serves position-addressed steps like the full cache."""
+
+    def __init__(self, max_batch_size, n_heads, head_dim, dtype=torch.bfloat16, **kwargs):
+        if n_heads != 1:
+            raise ValueError("a latent cache has one row per position for all heads")
+        super().__init__(max_batch_size, n_heads, head_dim, dtype, **kwargs)
+
+    def latent_rows(self, n):
+        """[n, rank + rot] view of the rows of positions 0 .. n-1."""
+        return self.k_cache[0, 0, :n]
+
+    def sequence_append(self, k_new, v_new, input_pos):
+        """Appends T rows at positions input_pos[0] ... (prompt portions attend over expanded rows, then store the latents)."""
+        from . import seq_ops
+        seq_ops.cache_append(k_new, v_new, self.k_cache, self.v_cache, self.pos, self.mask, self.cache_cts, input_pos)
+
+
+class RecurrentState(nn.Module):
+    """What a sequence carries from token to token besides key/value rows: `vectors` fp32 [n_vectors, width]
+    (previous-token activations for token shift) and, for a layer with a matrix-state recurrence, `matrix` fp32
+    [n_heads, head_dim, head_dim].  Fixed size whatever the sequence length; `reset` gives it back (all zero = the
+    state before the first token).  Built through `get_cache_constructor("state")` like the caches."""
+    relevant_kwargs = ["state_vectors", "state_width", "max_seq_length"]
+
+    def __init__(self, max_batch_size, n_heads, head_dim, dtype=torch.float32, state_vectors=1, state_width=0, **kwargs):
+        super().__init__()
+        if max_batch_size != 1:
+            raise NotImplementedError("batch size is fixed to 1 (reference model.py:188-189)")
+        self.n_heads, self.head_dim = int(n_heads), int(head_dim)
+        self.max_cache_length = 0   # holds no positions
+        self.register_buffer("vectors", torch.zeros(int(state_vectors), int(state_width), dtype=torch.float32))
+        self.register_buffer("matrix", torch.zeros(self.n_heads, self.head_dim, self.head_dim, dtype=torch.float32)
+                             if n_heads else torch.zeros(0, dtype=torch.float32))
+
+    def reset(self):
+        self.vectors.zero_()
+        self.matrix.zero_()
+
+    def memory_usage(self):
+        return (self.vectors.numel() + self.matrix.numel()) * 4 / (1024 ** 3)
+
+
 # --------------------------------------------------------------------------- registry
 
 _REGISTRY = {
+    "latent": KVCacheLatent, "state": RecurrentState,
     "full": KVCacheFull, "l2": KVCacheL2, "random": KVCacheRandom, "recent_global": KVCacheRecentGlobal,
     "heavy_hitter": KVCacheHeavyHitter, "hybrid": KVCacheHybrid, "keep_it_odd": KVCacheKeepItOdd,
 }

@@ -59,6 +59,9 @@ def _builtin():
     if "Tidelorn" not in MODEL_REGISTRY:
         from .tidelorn import TidelornTransformer
         register_model("Tidelorn", TidelornTransformer.from_config)
+    if "Detatar" not in MODEL_REGISTRY:
+        from .detatar import DetatarTransformer
+        register_model("Detatar", DetatarTransformer.from_config)
 
 
 def is_checkpoint_folder(path) -> bool:

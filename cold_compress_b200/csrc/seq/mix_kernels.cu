@@ -1,0 +1,749 @@
+// mix_kernels.cu -- sequence kernels for layers that carry per-sequence state besides a key/value cache
+// (include/cc_b200_seq.h, second part): grouped RMS norm fused with a gated residual sum, token shift, a
+// matrix-state linear recurrence with per-channel decay and a current-token bonus, the row preparation of latent
+// (low-rank) attention, per-head products for its absorbed one-token form, gated units, and the routing, dispatch and
+// combination of a mixture of experts.
+//
+// Arithmetic rule (as in seq_kernels.cu): norms, gates, angles, decays, the recurrent state, router scores and the
+// residual stream are fp32 whatever the storage type; expf / tanhf / sincosf are the accurate versions.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../../include/cc_b200_seq.h"
+
+namespace ccs {
+int fail(int code, const char* msg);
+int cuda_check(const char* where);
+}  // namespace ccs
+
+namespace ccm {
+using ccs::cuda_check;
+using ccs::fail;
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float ldf(const float* p, size_t i) { return p[i]; }
+__device__ __forceinline__ float ldf(const bf16* p, size_t i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void stf(float* p, size_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void stf(bf16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// Sum over the block in a fixed order (warp shuffles, then the warps' partial sums one after another).
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float s = 0.f;
+    for (int i = 0; i < nw; ++i) s += red[i];
+    return s;
+}
+
+__device__ __forceinline__ void load8(const float* p, float* o) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float* o) {
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+    const bf16* e = reinterpret_cast<const bf16*>(&u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = __bfloat162float(e[i]);
+}
+// One weight row against one input row, by a warp: eight elements per lane and load when both rows allow it.
+template <typename WT, typename XT>
+__device__ __forceinline__ float warp_dot(const WT* __restrict__ w, const XT* __restrict__ x, int K, int lane) {
+    float acc = 0.f;
+    if (K % 8 == 0 && (((uintptr_t)w | (uintptr_t)x) & 15) == 0) {
+#pragma unroll 2
+        for (int k = lane * 8; k < K; k += 256) {
+            float a[8], b[8];
+            load8(w + k, a);
+            load8(x + k, b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc = fmaf(a[i], b[i], acc);
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(ldf(w, k), ldf(x, k), acc);
+    }
+    return warp_sum(acc);
+}
+
+__device__ __forceinline__ float unit_act(float z, int kind) {
+    switch (kind) {
+        case CC_ACT_GELU_TANH: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        case CC_ACT_SILU: return z * sigmoidf_(z);
+        case CC_ACT_TANH: return tanhf(z);
+        case CC_ACT_SIGMOID: return sigmoidf_(z);
+        default: return z;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ embedding rows
+template <typename ST>
+__global__ void embed_rows_kernel(const int32_t* __restrict__ tokens, const ST* __restrict__ embed, float* __restrict__ x,
+                                  int E, float scale) {
+    const int t = blockIdx.x;
+    const size_t row = (size_t)tokens[t] * E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) x[(size_t)t * E + e] = ldf(embed, row + e) * scale;
+}
+
+// ------------------------------------------------------------------------------------------------ gated sum + grouped norm
+// One token per CTA: x += a * sigmoid(ga + ba) + b * sigmoid(gb + bb), then h = x / rms(x within its group) * w.
+template <typename ST>
+__global__ void __launch_bounds__(256) gated_group_norm_kernel(const CcSeqGatedNorm g) {
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    const int i = blockIdx.x, E = g.E, tid = threadIdx.x;
+    const size_t t = g.rows ? (size_t)g.rows[i] : (size_t)i;
+    float* x = g.x + t * E;
+    for (int e = tid; e < E; e += blockDim.x) {
+        float v = x[e];
+        if (g.a != nullptr) {
+            const float gate = g.ga ? sigmoidf_(g.ga[t * g.ldga + e] + (g.ba ? g.ba[e] : 0.f)) : 1.f;
+            v += g.a[t * g.lda + e] * gate;
+        }
+        if (g.b != nullptr) {
+            const float gate = g.gb ? sigmoidf_(g.gb[t * g.ldgb + e] + (g.bb ? g.bb[e] : 0.f)) : 1.f;
+            v += g.b[t * g.ldb + e] * gate;
+        }
+        row[e] = v;
+        if (g.a != nullptr || g.b != nullptr) x[e] = v;
+    }
+    __syncthreads();
+    if (g.w == nullptr) return;
+    const int gs = E / g.groups;
+    for (int grp = 0; grp < g.groups; ++grp) {
+        float ss = 0.f;
+        for (int e = tid; e < gs; e += blockDim.x) { const float v = row[grp * gs + e]; ss += v * v; }
+        const float rinv = 1.0f / sqrtf(block_sum(ss, red) / (float)gs + g.eps);
+        for (int e = tid; e < gs; e += blockDim.x) {
+            const int c = grp * gs + e;
+            const float h = row[c] * rinv * g.w[c];
+            if (g.h != nullptr) g.h[(size_t)i * E + c] = h;
+            if (g.h_act != nullptr) stf((ST*)g.h_act, (size_t)i * E + c, h);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ token shift
+// out[s][t] = h[t] + (h[t-1] - h[t]) * mu[s]; the row before the first one is the sequence's state, which then
+// becomes the last row.  Thread e alone reads and writes state[e].
+template <typename ST>
+__global__ void token_shift_kernel(const float* __restrict__ h, float* state, const float* __restrict__ mu,
+                                   ST* __restrict__ out, float* __restrict__ outf, int T, int E, int n) {
+    const int t = blockIdx.x;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const float cur = h[(size_t)t * E + e];
+        const float prev = t > 0 ? h[(size_t)(t - 1) * E + e] : state[e];
+        for (int s = 0; s < n; ++s) {
+            const float m = cur + (prev - cur) * mu[(size_t)s * E + e];
+            if (out != nullptr) stf(out, ((size_t)s * T + t) * E + e, m);
+            if (outf != nullptr && s == 0) outf[(size_t)t * E + e] = m;
+        }
+        if (t == 0) state[e] = h[(size_t)(T - 1) * E + e];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ gated unit
+template <typename ST>
+__global__ void gated_unit_kernel(const float* __restrict__ in, int64_t ld, int off_gate, int off_up, ST* __restrict__ out,
+                                  int T, int F, int kind) {
+    const size_t total = (size_t)T * F;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / F, f = idx - t * F;
+        float v = unit_act(in[t * ld + off_gate + f], kind);
+        if (off_up >= 0) v *= in[t * ld + off_up + f];
+        stf(out, idx, v);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ latent attention rows
+// One token per CTA.  From the fused down-projection row: the query latent and the key/value latent are RMS-normed
+// (plain weights); the trailing `rot_dim` columns are the key part shared by all heads, rotated by the position.
+template <typename ST>
+__global__ void __launch_bounds__(256) latent_prepare_kernel(const CcSeqLatentPrep a) {
+    __shared__ float red[32];
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const float* in = a.in + (size_t)t * a.ld;
+    const int Dk = a.kv_rank + a.rot_dim;
+    if (a.q_rank > 0) {
+        float ss = 0.f;
+        for (int e = tid; e < a.q_rank; e += blockDim.x) { const float v = in[a.off_q + e]; ss += v * v; }
+        const float rinv = 1.0f / sqrtf(block_sum(ss, red) / (float)a.q_rank + a.eps);
+        for (int e = tid; e < a.q_rank; e += blockDim.x)
+            stf((ST*)a.cq, (size_t)t * a.q_rank + e, in[a.off_q + e] * rinv * a.wq[e]);
+    }
+    float ss = 0.f;
+    for (int e = tid; e < a.kv_rank; e += blockDim.x) { const float v = in[a.off_kv + e]; ss += v * v; }
+    const float rinv = 1.0f / sqrtf(block_sum(ss, red) / (float)a.kv_rank + a.eps);
+    for (int e = tid; e < a.kv_rank; e += blockDim.x) {
+        const float c = in[a.off_kv + e] * rinv * a.wkv[e];
+        stf((ST*)a.krow, (size_t)t * Dk + e, c);
+        if (a.vrow != nullptr) stf((ST*)a.vrow, (size_t)t * a.kv_rank + e, c);
+    }
+    const float p = (float)(a.input_pos[0] + t);
+    const float* tail = in + a.off_kv + a.kv_rank;
+    const int half = a.rot_dims / 2;
+    ST* kr = (ST*)a.krow + (size_t)t * Dk + a.kv_rank;
+    for (int e = tid; e < half; e += blockDim.x) {
+        float sn, cs;
+        sincosf(p * a.inv_freq[e], &sn, &cs);
+        const float u = tail[e], v = tail[e + half];
+        stf(kr, e, u * cs - v * sn);
+        stf(kr, e + half, v * cs + u * sn);
+    }
+    for (int e = 2 * half + tid; e < a.rot_dim; e += blockDim.x) stf(kr, e, tail[e]);
+}
+
+// Rotation of one segment of every head of a fused query row, in place; optionally the rotated segment is also
+// copied to `tail` (the absorbed query layout [H, tail_ld] at column tail_off).
+__global__ void rope_heads_kernel(float* __restrict__ q, int64_t ld, const int32_t* __restrict__ input_pos,
+                                  const float* __restrict__ inv_freq, int H, int head_w, int off, int seg, int dims,
+                                  float* __restrict__ tail, int64_t tail_ld, int tail_off, int T) {
+    const int t = blockIdx.x, half = dims / 2;
+    const float p = (float)(input_pos[0] + t);
+    float* row = q + (size_t)t * ld;
+    for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
+        const int h = idx / half, e = idx - h * half;
+        float* s = row + (size_t)h * head_w + off;
+        float sn, cs;
+        sincosf(p * inv_freq[e], &sn, &cs);
+        const float u = s[e], v = s[e + half];
+        s[e] = u * cs - v * sn;
+        s[e + half] = v * cs + u * sn;
+    }
+    if (tail == nullptr) return;
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < H * seg; idx += blockDim.x) {
+        const int h = idx / seg, e = idx - h * seg;
+        tail[((size_t)t * H + h) * tail_ld + tail_off + e] = row[(size_t)h * head_w + off + e];
+    }
+}
+
+// Per-head key and value rows from the up-projection of the latents: row n < n_old goes into the head-major
+// "old" buffers [H, n_old, *], the others into the token-major "new" buffers [T, H, *].  The key row of head h is
+// [up-projected part | shared rotated part of the latent row].
+template <typename ST>
+__global__ void latent_expand_kernel(const CcSeqLatentExpand a) {
+    const int n = blockIdx.x, H = a.H, D = a.D, V = a.V, R = a.R, Dk = D + R;
+    const bool old = n < a.n_old;
+    const int r = old ? n : n - a.n_old;
+    const float* kv = old ? a.kv_old + (size_t)r * a.ld_kv : a.kv_new + (size_t)r * a.ld_kv;
+    const ST* lat = old ? (const ST*)a.lat_old + (size_t)r * a.ld_lat : (const ST*)a.lat_new + (size_t)r * a.ld_lat;
+    for (int idx = threadIdx.x; idx < H * Dk; idx += blockDim.x) {
+        const int h = idx / Dk, e = idx - h * Dk;
+        const float v = e < D ? kv[(size_t)h * D + e] : ldf(lat, a.kv_rank + e - D);
+        if (old) stf((ST*)a.k_old, ((size_t)h * a.n_old + r) * Dk + e, v);
+        else stf((ST*)a.k_new, ((size_t)r * H + h) * Dk + e, v);
+    }
+    for (int idx = threadIdx.x; idx < H * V; idx += blockDim.x) {
+        const int h = idx / V, e = idx - h * V;
+        const float v = kv[(size_t)H * D + (size_t)h * V + e];
+        if (old) stf((ST*)a.v_old, ((size_t)h * a.n_old + r) * V + e, v);
+        else stf((ST*)a.v_new, ((size_t)r * H + h) * V + e, v);
+    }
+}
+
+// y [T, H, V] *= sigmoid(g[t, h])
+template <typename ST>
+__global__ void head_gate_kernel(ST* __restrict__ y, const float* __restrict__ g, int64_t ldg, int T, int H, int V) {
+    const size_t total = (size_t)T * H * V;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t th = idx / V, t = th / H, h = th - t * H;
+        stf(y, idx, ldf(y, idx) * sigmoidf_(g[t * ldg + h]));
+    }
+}
+
+// out[h, n] = W[h, n, :] . x[h, :]  (* sigmoid(gate[h])): a block-diagonal one-token product, a warp per row.
+template <typename WT, typename XT, typename OT>
+__global__ void __launch_bounds__(256) head_gemv_kernel(const WT* __restrict__ W, const XT* __restrict__ x, int64_t sx,
+                                                        OT* __restrict__ out, int64_t so, const float* __restrict__ gate,
+                                                        int H, int N, int K) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + warp;
+    if (row >= H * N) return;
+    const int h = row / N, n = row - h * N;
+    float acc = warp_dot<WT, XT>(W + ((size_t)h * N + n) * K, x + (size_t)h * sx, K, lane);
+    if (lane == 0) {
+        if (gate != nullptr) acc *= sigmoidf_(gate[h]);
+        stf(out, (size_t)h * so + n, acc);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ matrix-state recurrence
+// Per head a state S [D, D] (key channel i, value channel j):  o_t[j] = sum_i r_t[i] (S[i][j] + u[i] k_t[i] v_t[j]),
+// then S[i][j] <- w_t[i] S[i][j] + k_t[i] v_t[j], with w_t = exp(-exp(wraw_t + w0)).  A CTA owns WKV_J value
+// channels of one head; thread (part, j) keeps WKV_CH rows of column j in registers.  Tokens are staged WKV_TB at a
+// time; the parts' partial outputs meet in shared memory after each batch, summed in part order, so the arithmetic of
+// a token does not depend on how the sequence was cut into launches.
+constexpr int WKV_J = 32, WKV_CH = 16, WKV_TB = 16;
+
+__global__ void wkv_kernel(const CcSeqWkv a) {
+    extern __shared__ float sm[];
+    const int D = a.D, P = (D + WKV_CH - 1) / WKV_CH;
+    float* rs = sm;                       // [TB][D]
+    float* ks = rs + WKV_TB * D;
+    float* ws = ks + WKV_TB * D;
+    float* vs = ws + WKV_TB * D;          // [TB][J]
+    float* us = vs + WKV_TB * WKV_J;      // [D]
+    float* part = us + D;                 // [TB][P][J]
+    const int h = blockIdx.x, j0 = blockIdx.y * WKV_J;
+    const int tid = threadIdx.x, nth = blockDim.x, jl = tid % WKV_J, p = tid / WKV_J, j = j0 + jl;
+    const int i0 = p * WKV_CH;
+    const size_t HD = (size_t)a.H * D;
+    float* S = a.state + (size_t)h * D * D;
+    float st[WKV_CH];
+#pragma unroll
+    for (int c = 0; c < WKV_CH; ++c) st[c] = (i0 + c < D && j < D) ? S[(size_t)(i0 + c) * D + j] : 0.f;
+    for (int i = tid; i < D; i += nth) us[i] = a.u[(size_t)h * D + i];
+    for (int tb = 0; tb < a.T; tb += WKV_TB) {
+        const int nt = min(WKV_TB, a.T - tb);
+        __syncthreads();
+        for (int idx = tid; idx < nt * D; idx += nth) {
+            const int t = idx / D, i = idx - t * D;
+            const size_t src = (size_t)(tb + t) * HD + (size_t)h * D + i;
+            rs[idx] = a.r[src];
+            ks[idx] = a.k[src];
+            ws[idx] = expf(-expf(a.wraw[src] + a.w0[(size_t)h * D + i]));
+        }
+        for (int idx = tid; idx < nt * WKV_J; idx += nth) {
+            const int t = idx / WKV_J, c = idx - t * WKV_J;
+            vs[idx] = j0 + c < D ? a.v[(size_t)(tb + t) * HD + (size_t)h * D + j0 + c] : 0.f;
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const float v = vs[t * WKV_J + jl];
+            const float* r = rs + t * D + i0;
+            const float* k = ks + t * D + i0;
+            const float* w = ws + t * D + i0;
+            float acc = 0.f;
+#pragma unroll
+            for (int c = 0; c < WKV_CH; ++c) {
+                if (i0 + c < D) {
+                    const float kv = k[c] * v;
+                    acc = fmaf(r[c], fmaf(us[i0 + c], kv, st[c]), acc);
+                    st[c] = fmaf(w[c], st[c], kv);
+                }
+            }
+            part[(t * P + p) * WKV_J + jl] = acc;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < nt * WKV_J; idx += nth) {
+            const int t = idx / WKV_J, c = idx - t * WKV_J;
+            if (j0 + c >= D) continue;
+            float o = 0.f;
+            for (int q = 0; q < P; ++q) o += part[(t * P + q) * WKV_J + c];
+            a.o[(size_t)(tb + t) * HD + (size_t)h * D + j0 + c] = o;
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < WKV_CH; ++c)
+        if (i0 + c < D && j < D) S[(size_t)(i0 + c) * D + j] = st[c];
+}
+
+// out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * nw[h, :] * silu(graw[t, h, :]); a warp per (token, head).
+template <typename ST>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ graw, int64_t ldg,
+                                      const float* __restrict__ nw, ST* __restrict__ out, int T, int H, int D, float eps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t th = (size_t)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (th >= (size_t)T * H) return;
+    const size_t t = th / H, h = th - t * H;
+    const float* row = o + th * D;
+    float ss = 0.f;
+    for (int e = lane; e < D; e += 32) ss += row[e] * row[e];
+    const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
+    for (int e = lane; e < D; e += 32) {
+        const float g = graw[t * ldg + h * D + e];
+        stf(out, th * D + e, row[e] * rinv * nw[h * D + e] * (g * sigmoidf_(g)));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ mixture of experts
+// A warp per token.  Scores = softmax of the router logits over all outputs; choice = score + correction; experts
+// outside the `keep` best groups (group score = its largest choice) cannot be chosen; the `top` largest choices win
+// (the lower index on a tie); weights = the winners' scores divided by their sum.
+__global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, const float* __restrict__ correction,
+                                 int32_t* __restrict__ ids, float* __restrict__ wts, int T, int n, int groups, int keep, int top) {
+    extern __shared__ float smr[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int t = blockIdx.x * nw + warp;
+    float* s = smr + (size_t)warp * (2 * n + groups);
+    float* c = s + n;
+    float* gm = c + n;
+    if (t >= T) return;
+    const float* z = logits + (size_t)t * ld;
+    float mx = -INFINITY;
+    for (int i = lane; i < n; i += 32) mx = fmaxf(mx, z[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int i = lane; i < n; i += 32) { const float e = expf(z[i] - mx); s[i] = e; sum += e; }
+    sum = warp_sum(sum);
+    for (int i = lane; i < n; i += 32) { s[i] = s[i] / sum; c[i] = s[i] + (correction ? correction[i] : 0.f); }
+    __syncwarp();
+    if (groups > 1 && keep < groups) {
+        const int gs = n / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float m = -INFINITY;
+            for (int i = 0; i < gs; ++i) m = fmaxf(m, c[g * gs + i]);
+            gm[g] = m;
+        }
+        __syncwarp();
+        if (lane == 0) {   // the `keep` best groups are marked with NaN-free +inf, the others stay
+            for (int kk = 0; kk < keep; ++kk) {
+                int best = -1;
+                float bv = -INFINITY;
+                for (int g = 0; g < groups; ++g)
+                    if (gm[g] != INFINITY && (best < 0 || gm[g] > bv)) { best = g; bv = gm[g]; }
+                if (best >= 0) gm[best] = INFINITY;
+            }
+        }
+        __syncwarp();
+        for (int i = lane; i < n; i += 32)
+            if (gm[i / gs] != INFINITY) c[i] = -INFINITY;
+        __syncwarp();
+    }
+    float wsum = 0.f;
+    for (int kk = 0; kk < top; ++kk) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = lane; i < n; i += 32) {
+            const float v = c[i];
+            if (v > bv || (v == bv && i < bi && v != -INFINITY)) { bv = v; bi = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (bi >= n) bi = 0;   // fewer choosable experts than `top`: a configuration error, kept harmless
+        if (lane == 0) {
+            ids[(size_t)t * top + kk] = bi;
+            wts[(size_t)t * top + kk] = s[bi];
+            c[bi] = -INFINITY;
+        }
+        wsum += s[bi];
+        __syncwarp();
+    }
+    __syncwarp();
+    for (int kk = lane; kk < top; kk += 32) wts[(size_t)t * top + kk] = wts[(size_t)t * top + kk] / (wsum + 1e-20f);
+}
+
+// Groups the (token, choice) pairs of the real experts by expert: counts[e], and for every pair its row `slot` in the
+// grouped order (-1 for an identity expert) with the row's token in perm[slot].  One CTA.
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* __restrict__ ids, int M, int top, int n_real,
+                                                         int32_t* __restrict__ counts, int32_t* __restrict__ slot,
+                                                         int32_t* __restrict__ perm) {
+    extern __shared__ int smi[];
+    int* cnt = smi;             // [n_real]
+    int* off = cnt + n_real;    // [n_real]
+    for (int e = threadIdx.x; e < n_real; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int m = threadIdx.x; m < M; m += blockDim.x) {
+        const int e = ids[m];
+        if (e < n_real) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < n_real; ++e) { off[e] = run; run += cnt[e]; }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_real; e += blockDim.x) { counts[e] = cnt[e]; cnt[e] = 0; }
+    __syncthreads();
+    for (int m = threadIdx.x; m < M; m += blockDim.x) {
+        const int e = ids[m];
+        if (e < n_real) {
+            const int s = off[e] + atomicAdd(&cnt[e], 1);
+            slot[m] = s;
+            perm[s] = m / top;
+        } else {
+            slot[m] = -1;
+        }
+    }
+}
+
+template <typename ST>
+__global__ void gather_rows_kernel(const ST* __restrict__ src, const int32_t* __restrict__ perm, ST* __restrict__ dst, int E) {
+    const size_t m = blockIdx.x;
+    const ST* s = src + (size_t)perm[m] * E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) dst[m * E + e] = s[e];
+}
+
+// One-token form of the experts: a block of 8 warps takes 8 rows of the chosen expert's gate and up matrices for
+// one (token, choice) pair: act = silu(gate . h) * (up . h).  Pairs that chose an identity expert are skipped.
+template <typename ST>
+__global__ void __launch_bounds__(256) moe_expert_up_kernel(const ST* __restrict__ Wgu, const ST* __restrict__ h,
+                                                            const int32_t* __restrict__ ids, ST* __restrict__ act,
+                                                            int n_real, int F, int E, int kind, int top) {
+    const int m = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = ids[m];
+    const int f = blockIdx.x * 8 + warp;
+    if (e >= n_real || f >= F) return;
+    const int t = m / top;
+    const ST* x = h + (size_t)t * E;
+    const ST* wg = Wgu + ((size_t)e * 2 * F + f) * E;
+    const float g = warp_dot<ST, ST>(wg, x, E, lane);
+    const float u = warp_dot<ST, ST>(wg + (size_t)F * E, x, E, lane);
+    if (lane == 0) stf(act, (size_t)m * F + f, unit_act(g, kind) * u);
+}
+
+template <typename ST>
+__global__ void __launch_bounds__(256) moe_expert_down_kernel(const ST* __restrict__ Wd, const ST* __restrict__ act,
+                                                              const int32_t* __restrict__ ids, float* __restrict__ y,
+                                                              int n_real, int F, int E) {
+    const int m = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = ids[m];
+    const int n = blockIdx.x * 8 + warp;
+    if (e >= n_real || n >= E) return;
+    const float v = warp_dot<ST, ST>(Wd + ((size_t)e * E + n) * F, act + (size_t)m * F, F, lane);
+    if (lane == 0) y[(size_t)m * E + n] = v;
+}
+
+// out[t] = sum_k w[t,k] * (expert row | h[t] for an identity expert) + sigmoid(sg[t]) * shared[t]
+__global__ void moe_combine_kernel(const CcSeqMoeCombine a) {
+    const int t = blockIdx.x, E = a.E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < a.top; ++k) {
+            const size_t m = (size_t)t * a.top + k;
+            const float w = a.wts[m];
+            if (a.ids[m] >= a.n_real) acc += w * a.h[(size_t)t * E + e];
+            else acc += w * a.y[(size_t)(a.slot ? a.slot[m] : (int)m) * E + e];
+        }
+        if (a.shared != nullptr) {
+            const float g = a.sg ? sigmoidf_(a.sg[(size_t)t * a.ld_sg]) : 1.f;
+            acc += g * a.shared[(size_t)t * E + e];
+        }
+        a.out[(size_t)t * E + e] = acc;
+    }
+}
+
+static int blocks_for(size_t total, int threads) {
+    size_t b = (total + threads - 1) / threads;
+    return (int)(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
+}
+
+}  // namespace ccm
+
+using namespace ccm;
+
+#define CCM_ST(dt, CALL)                                                \
+    do {                                                                \
+        if ((dt) == CC_DT_F32) { CALL(float); }                         \
+        else if ((dt) == CC_DT_BF16) { CALL(bf16); }                    \
+        else return fail(CC_SEQ_ERR_INVALID_ARG, "unknown element type"); \
+    } while (0)
+
+extern "C" {
+
+int cc_seq_embed_rows(const int32_t* tokens, const void* embed, int32_t table_dtype, float* x, int32_t T, int32_t E,
+                      float scale, void* stream) {
+    if (!tokens || !embed || !x || T < 1 || E < 1) return fail(CC_SEQ_ERR_INVALID_ARG, "embed_rows: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(ST) embed_rows_kernel<ST><<<T, 256, 0, st>>>(tokens, (const ST*)embed, x, E, scale)
+    CCM_ST(table_dtype, CALL);
+#undef CALL
+    return cuda_check("embed_rows_kernel");
+}
+
+int cc_seq_gated_group_norm(const CcSeqGatedNorm* g, void* stream) {
+    if (!g || !g->x || g->T < 1 || g->E < 1 || g->groups < 1 || g->E % g->groups)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "gated_group_norm: bad argument");
+    const size_t smem = sizeof(float) * (size_t)g->E;
+    if (smem > 200 * 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "gated_group_norm: rows longer than 51200");
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(ST)                                                                                                     \
+    {                                                                                                                \
+        auto kern = gated_group_norm_kernel<ST>;                                                                     \
+        static size_t configured = 48 * 1024;                                                                        \
+        if (smem > configured) {                                                                                     \
+            configured = smem;                                                                                       \
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)   \
+                return cuda_check("gated_group_norm: shared memory");                                                \
+        }                                                                                                            \
+        kern<<<g->T, 256, smem, st>>>(*g);                                                                           \
+    }
+    CCM_ST(g->act_dtype, CALL);
+#undef CALL
+    return cuda_check("gated_group_norm_kernel");
+}
+
+int cc_seq_token_shift(const float* h, float* state, const float* mu, void* out, int32_t out_dtype, float* outf,
+                       int32_t T, int32_t E, int32_t n, void* stream) {
+    if (!h || !state || !mu || T < 1 || E < 1 || n < 1 || (!out && !outf))
+        return fail(CC_SEQ_ERR_INVALID_ARG, "token_shift: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(ST) token_shift_kernel<ST><<<T, 256, 0, st>>>(h, state, mu, (ST*)out, outf, T, E, n)
+    CCM_ST(out_dtype, CALL);
+#undef CALL
+    return cuda_check("token_shift_kernel");
+}
+
+int cc_seq_gated_unit(const float* in, int64_t ld, int32_t off_gate, int32_t off_up, void* out, int32_t out_dtype,
+                      int32_t T, int32_t F, int32_t kind, void* stream) {
+    if (!in || !out || T < 1 || F < 1 || kind < CC_ACT_NONE || kind > CC_ACT_SIGMOID)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "gated_unit: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nb = blocks_for((size_t)T * F, 256);
+#define CALL(ST) gated_unit_kernel<ST><<<nb, 256, 0, st>>>(in, ld, off_gate, off_up, (ST*)out, T, F, kind)
+    CCM_ST(out_dtype, CALL);
+#undef CALL
+    return cuda_check("gated_unit_kernel");
+}
+
+int cc_seq_latent_prepare(const CcSeqLatentPrep* a, void* stream) {
+    if (!a || !a->in || !a->krow || !a->wkv || !a->input_pos || a->T < 1 || a->kv_rank < 1 || a->rot_dim < 0 ||
+        a->rot_dims < 0 || a->rot_dims > a->rot_dim || (a->rot_dims & 1) || (a->rot_dims && !a->inv_freq) ||
+        (a->q_rank > 0 && (!a->cq || !a->wq)))
+        return fail(CC_SEQ_ERR_INVALID_ARG, "latent_prepare: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(ST) latent_prepare_kernel<ST><<<a->T, 256, 0, st>>>(*a)
+    CCM_ST(a->dtype, CALL);
+#undef CALL
+    return cuda_check("latent_prepare_kernel");
+}
+
+int cc_seq_rope_heads(float* q, int64_t ld, const int32_t* input_pos, const float* inv_freq, int32_t T, int32_t H,
+                      int32_t head_w, int32_t off, int32_t seg, int32_t dims, float* tail, int64_t tail_ld,
+                      int32_t tail_off, void* stream) {
+    if (!q || !input_pos || T < 1 || H < 1 || dims < 0 || (dims & 1) || dims > seg || off + seg > head_w ||
+        (dims && !inv_freq))
+        return fail(CC_SEQ_ERR_INVALID_ARG, "rope_heads: bad argument");
+    rope_heads_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(q, ld, input_pos, inv_freq, H, head_w, off, seg, dims, tail,
+                                                           tail_ld, tail_off, T);
+    return cuda_check("rope_heads_kernel");
+}
+
+int cc_seq_latent_expand(const CcSeqLatentExpand* a, void* stream) {
+    if (!a || a->n_old < 0 || a->n_new < 0 || a->n_old + a->n_new < 1 || a->H < 1 || a->D < 0 || a->V < 1 || a->R < 0 ||
+        (a->n_old && (!a->kv_old || !a->lat_old || !a->k_old || !a->v_old)) ||
+        (a->n_new && (!a->kv_new || !a->lat_new || !a->k_new || !a->v_new)))
+        return fail(CC_SEQ_ERR_INVALID_ARG, "latent_expand: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(ST) latent_expand_kernel<ST><<<a->n_old + a->n_new, 256, 0, st>>>(*a)
+    CCM_ST(a->dtype, CALL);
+#undef CALL
+    return cuda_check("latent_expand_kernel");
+}
+
+int cc_seq_head_gate(void* y, int32_t dtype, const float* g, int64_t ldg, int32_t T, int32_t H, int32_t V, void* stream) {
+    if (!y || !g || T < 1 || H < 1 || V < 1) return fail(CC_SEQ_ERR_INVALID_ARG, "head_gate: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nb = blocks_for((size_t)T * H * V, 256);
+#define CALL(ST) head_gate_kernel<ST><<<nb, 256, 0, st>>>((ST*)y, g, ldg, T, H, V)
+    CCM_ST(dtype, CALL);
+#undef CALL
+    return cuda_check("head_gate_kernel");
+}
+
+int cc_seq_head_gemv(const void* W, int32_t w_dtype, const void* x, int32_t x_dtype, int64_t sx, void* out,
+                     int32_t out_dtype, int64_t so, const float* gate, int32_t H, int32_t N, int32_t K, void* stream) {
+    if (!W || !x || !out || H < 1 || N < 1 || K < 1) return fail(CC_SEQ_ERR_INVALID_ARG, "head_gemv: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nb = (H * N + 7) / 8;
+    const bool wb = w_dtype == CC_DT_BF16, xb = x_dtype == CC_DT_BF16, ob = out_dtype == CC_DT_BF16;
+#define HG(WT, XT, OT) head_gemv_kernel<WT, XT, OT><<<nb, 256, 0, st>>>((const WT*)W, (const XT*)x, sx, (OT*)out, so, gate, H, N, K)
+    if (wb && xb && ob) HG(bf16, bf16, bf16);
+    else if (wb && xb && !ob) HG(bf16, bf16, float);
+    else if (wb && !xb && ob) HG(bf16, float, bf16);
+    else if (wb && !xb && !ob) HG(bf16, float, float);
+    else if (!wb && !xb && !ob) HG(float, float, float);
+    else return fail(CC_SEQ_ERR_INVALID_ARG, "head_gemv: unsupported combination of element types");
+#undef HG
+    return cuda_check("head_gemv_kernel");
+}
+
+int cc_seq_wkv(const CcSeqWkv* a, void* stream) {
+    if (!a || !a->r || !a->k || !a->v || !a->wraw || !a->w0 || !a->u || !a->state || !a->o || a->T < 1 || a->H < 1 || a->D < 1)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "wkv: bad argument");
+    const int P = (a->D + WKV_CH - 1) / WKV_CH;
+    if (P * WKV_J > 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "wkv: head size above 512");
+    const size_t smem = sizeof(float) * ((size_t)3 * WKV_TB * a->D + (size_t)WKV_TB * WKV_J + a->D + (size_t)WKV_TB * P * WKV_J);
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        configured = smem;
+        if (cudaFuncSetAttribute(wkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return cuda_check("wkv: shared memory");
+    }
+    dim3 grid(a->H, (a->D + WKV_J - 1) / WKV_J);
+    wkv_kernel<<<grid, P * WKV_J, smem, (cudaStream_t)stream>>>(*a);
+    return cuda_check("wkv_kernel");
+}
+
+int cc_seq_head_norm_gate(const float* o, const float* graw, int64_t ldg, const float* nw, void* out, int32_t out_dtype,
+                          int32_t T, int32_t H, int32_t D, float eps, void* stream) {
+    if (!o || !graw || !nw || !out || T < 1 || H < 1 || D < 1) return fail(CC_SEQ_ERR_INVALID_ARG, "head_norm_gate: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nb = (int)(((size_t)T * H + 7) / 8);
+#define CALL(ST) head_norm_gate_kernel<ST><<<nb, 256, 0, st>>>(o, graw, ldg, nw, (ST*)out, T, H, D, eps)
+    CCM_ST(out_dtype, CALL);
+#undef CALL
+    return cuda_check("head_norm_gate_kernel");
+}
+
+int cc_seq_moe_route(const float* logits, int64_t ld, const float* correction, int32_t* ids, float* wts, int32_t T,
+                     int32_t n, int32_t groups, int32_t keep, int32_t top, void* stream) {
+    if (!logits || !ids || !wts || T < 1 || n < 1 || groups < 1 || n % groups || keep < 1 || top < 1 || top > n)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "moe_route: bad argument");
+    const int warps = 4;
+    const size_t smem = sizeof(float) * (size_t)warps * (2 * n + groups);
+    if (smem > 48 * 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "moe_route: too many experts");
+    moe_route_kernel<<<(T + warps - 1) / warps, warps * 32, smem, (cudaStream_t)stream>>>(logits, ld, correction, ids, wts, T,
+                                                                                        n, groups, keep, top);
+    return cuda_check("moe_route_kernel");
+}
+
+int cc_seq_moe_group(const int32_t* ids, int32_t M, int32_t top, int32_t n_real, int32_t* counts, int32_t* slot,
+                     int32_t* perm, void* stream) {
+    if (!ids || !counts || !slot || !perm || M < 1 || top < 1 || n_real < 1 || n_real > 4096)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "moe_group: bad argument");
+    moe_group_kernel<<<1, 1024, sizeof(int) * 2 * n_real, (cudaStream_t)stream>>>(ids, M, top, n_real, counts, slot, perm);
+    return cuda_check("moe_group_kernel");
+}
+
+int cc_seq_gather_rows(const void* src, const int32_t* perm, void* dst, int32_t dtype, int32_t M, int32_t E, void* stream) {
+    if (!src || !perm || !dst || M < 1 || E < 1) return fail(CC_SEQ_ERR_INVALID_ARG, "gather_rows: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(ST) gather_rows_kernel<ST><<<M, 256, 0, st>>>((const ST*)src, perm, (ST*)dst, E)
+    CCM_ST(dtype, CALL);
+#undef CALL
+    return cuda_check("gather_rows_kernel");
+}
+
+int cc_seq_moe_expert_tokens(const void* Wgu, const void* Wd, const void* h, const int32_t* ids, void* act, float* y,
+                             int32_t dtype, int32_t T, int32_t top, int32_t n_real, int32_t F, int32_t E, int32_t kind,
+                             void* stream) {
+    if (!Wgu || !Wd || !h || !ids || !act || !y || T < 1 || top < 1 || F < 1 || E < 1 || (size_t)T * top > 65535)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "moe_expert_tokens: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    const dim3 gu((F + 7) / 8, T * top, 1), gd((E + 7) / 8, T * top, 1);
+#define CALL(ST)                                                                                                       \
+    {                                                                                                                  \
+        moe_expert_up_kernel<ST><<<gu, 256, 0, st>>>((const ST*)Wgu, (const ST*)h, ids, (ST*)act, n_real, F, E, kind, top); \
+        moe_expert_down_kernel<ST><<<gd, 256, 0, st>>>((const ST*)Wd, (const ST*)act, ids, y, n_real, F, E);           \
+    }
+    CCM_ST(dtype, CALL);
+#undef CALL
+    return cuda_check("moe_expert kernels");
+}
+
+int cc_seq_moe_combine(const CcSeqMoeCombine* a, void* stream) {
+    if (!a || !a->ids || !a->wts || !a->h || !a->out || a->T < 1 || a->E < 1 || a->top < 1)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "moe_combine: bad argument");
+    moe_combine_kernel<<<a->T, 256, 0, (cudaStream_t)stream>>>(*a);
+    return cuda_check("moe_combine_kernel");
+}
+
+}  // extern "C"

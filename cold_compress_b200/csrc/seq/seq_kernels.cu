@@ -16,12 +16,13 @@
 namespace ccs {
 
 static thread_local char g_err[512] = "";
-static int fail(int code, const char* msg) {
+// fail() and cuda_check() are shared with the other files of this library (declared there by hand)
+int fail(int code, const char* msg) {
     strncpy(g_err, msg, sizeof(g_err) - 1);
     g_err[sizeof(g_err) - 1] = 0;
     return code;
 }
-static int cuda_check(const char* where) {
+int cuda_check(const char* where) {
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) return CC_SEQ_OK;
     snprintf(g_err, sizeof(g_err), "%s: %s", where, cudaGetErrorString(e));

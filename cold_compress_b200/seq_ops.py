@@ -165,3 +165,227 @@ seq_attention = torch.ops.cold_compress_b200.seq_attention
 seq_residual_norm = torch.ops.cold_compress_b200.seq_residual_norm
 seq_clamped_glu = torch.ops.cold_compress_b200.seq_clamped_glu
 seq_gemv = torch.ops.cold_compress_b200.seq_gemv
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Second part of the C ABI (csrc/seq/mix_kernels.cu): state-carrying layers.  Plain functions over the same
+# library: every call enqueues on the current stream and reads positions, expert ids and state from device memory.
+# A "column range" argument is a 2-D fp32 view whose rows may be strided (a slice of a fused projection's output).
+
+def _cols(t):
+    """(pointer, row stride in elements) of a 2-D view with unit column stride."""
+    if t is None:
+        return None, 0
+    if not t.is_cuda:
+        raise _lib.CcError("cold_compress_b200 sequence ops run on CUDA tensors only (no CPU fallback)")
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise _lib.CcError("expected a 2-D view with contiguous columns")
+    return t.data_ptr(), t.stride(0)
+
+
+def _f32(name, t):
+    if t is not None and t.dtype != torch.float32:
+        raise _lib.CcError(f"{name}: expected fp32, got {t.dtype}")
+    return t
+
+
+def embed_rows(tokens, embed, x, scale):
+    _need(("tokens", tokens, torch.int32), ("embed", embed, None), ("x", x, torch.float32))
+    T, E = tokens.numel(), embed.shape[1]
+    assert x.shape == (T, E)
+    _lib.check_seq(_lib.load_seq().cc_seq_embed_rows(_p(tokens), _p(embed), _dt(embed), _p(x), T, E, float(scale), _stream()),
+                   "cc_seq_embed_rows")
+
+
+def gated_group_norm(x, w, groups, eps, h=None, h_act=None, a=None, ga=None, ba=None, b=None, gb=None, bb=None, rows=None):
+    """x (fp32 [*, E], in place) += a * sigmoid(ga + ba) + b * sigmoid(gb + bb); h / h_act = grouped RMS norm of it."""
+    _need(("x", x, torch.float32), ("w", w, torch.float32), ("h", h, torch.float32), ("h_act", h_act, None),
+          ("ba", ba, torch.float32), ("bb", bb, torch.float32), ("rows", rows, torch.int64))
+    g = _lib.CcSeqGatedNorm()
+    E = x.shape[-1]
+    g.x, g.w, g.h, g.h_act = _p(x), _p(w), _p(h), _p(h_act)
+    g.act_dtype = _dt(h_act) if h_act is not None else _lib.DT_F32
+    g.a, g.lda = _cols(_f32("a", a))
+    g.ga, g.ldga = _cols(_f32("ga", ga))
+    g.b, g.ldb = _cols(_f32("b", b))
+    g.gb, g.ldgb = _cols(_f32("gb", gb))
+    g.ba, g.bb, g.rows = _p(ba), _p(bb), _p(rows)
+    g.T = rows.numel() if rows is not None else x.numel() // E
+    g.E, g.groups, g.eps = E, int(groups), float(eps)
+    _lib.check_seq(_lib.load_seq().cc_seq_gated_group_norm(C.byref(g), _stream()), "cc_seq_gated_group_norm")
+
+
+def token_shift(h, state, mu, out=None, outf=None):
+    """out[s, t] = h[t] + (h[t-1] - h[t]) * mu[s] with h[-1] = state; state <- h[T-1]."""
+    _need(("h", h, torch.float32), ("state", state, torch.float32), ("mu", mu, torch.float32), ("out", out, None),
+          ("outf", outf, torch.float32))
+    T, E = h.shape
+    n = mu.numel() // E
+    assert state.numel() == E and (out is None or out.numel() == n * T * E)
+    _lib.check_seq(_lib.load_seq().cc_seq_token_shift(_p(h), _p(state), _p(mu), _p(out), _dt(out) if out is not None else _lib.DT_F32,
+                                                      _p(outf), T, E, n, _stream()), "cc_seq_token_shift")
+
+
+def gated_unit(src, off_gate, off_up, out, kind):
+    """out[t, f] = act(src[t, off_gate + f]) * src[t, off_up + f]  (off_up < 0: activation only)."""
+    _need(("out", out, None))
+    ptr, ld = _cols(_f32("src", src))
+    T, F = out.shape
+    _lib.check_seq(_lib.load_seq().cc_seq_gated_unit(ptr, ld, int(off_gate), int(off_up), _p(out), _dt(out), T, F, int(kind),
+                                                     _stream()), "cc_seq_gated_unit")
+
+
+def latent_prepare(src, off_q, q_rank, off_kv, kv_rank, rot_dim, rot_dims, wq, wkv, inv_freq, input_pos, cq, krow, vrow, eps):
+    _need(("wq", wq, torch.float32), ("wkv", wkv, torch.float32), ("inv_freq", inv_freq, torch.float32),
+          ("input_pos", input_pos, torch.int32), ("cq", cq, krow.dtype), ("krow", krow, None), ("vrow", vrow, krow.dtype))
+    a = _lib.CcSeqLatentPrep()
+    a.inp, a.ld = _cols(_f32("src", src))
+    a.off_q, a.q_rank, a.off_kv, a.kv_rank, a.rot_dim, a.rot_dims = int(off_q), int(q_rank), int(off_kv), int(kv_rank), int(rot_dim), int(rot_dims)
+    a.wq, a.wkv, a.inv_freq, a.input_pos = _p(wq), _p(wkv), _p(inv_freq), _p(input_pos)
+    a.cq, a.krow, a.vrow, a.dtype, a.T, a.eps = _p(cq), _p(krow), _p(vrow), _dt(krow), src.shape[0], float(eps)
+    _lib.check_seq(_lib.load_seq().cc_seq_latent_prepare(C.byref(a), _stream()), "cc_seq_latent_prepare")
+
+
+def rope_heads(q, input_pos, inv_freq, H, head_w, off, seg, dims, tail=None, tail_off=0):
+    """Rotates the segment [off, off + seg) of each of the H heads of q (fp32 [T, >= H * head_w]) in place."""
+    _need(("input_pos", input_pos, torch.int32), ("inv_freq", inv_freq, torch.float32), ("tail", tail, torch.float32))
+    ptr, ld = _cols(_f32("q", q))
+    _lib.check_seq(_lib.load_seq().cc_seq_rope_heads(ptr, ld, _p(input_pos), _p(inv_freq), q.shape[0], int(H), int(head_w), int(off),
+                                                     int(seg), int(dims), _p(tail), tail.shape[-1] if tail is not None else 0,
+                                                     int(tail_off), _stream()), "cc_seq_rope_heads")
+
+
+def latent_expand(kv_old, kv_new, lat_old, lat_new, k_old, v_old, k_new, v_new, H, D, V, R, kv_rank):
+    a = _lib.CcSeqLatentExpand()
+    a.kv_old, ld0 = _cols(_f32("kv_old", kv_old))
+    a.kv_new, ld1 = _cols(_f32("kv_new", kv_new))
+    a.ld_kv = ld1 or ld0
+    assert kv_old is None or kv_new is None or ld0 == ld1
+    a.lat_old, l0 = _cols(lat_old)
+    a.lat_new, l1 = _cols(lat_new)
+    a.ld_lat = l1 or l0
+    assert lat_old is None or lat_new is None or l0 == l1
+    ref = k_new if k_new is not None else k_old
+    _need(("k_old", k_old, ref.dtype), ("v_old", v_old, ref.dtype), ("k_new", k_new, ref.dtype), ("v_new", v_new, ref.dtype))
+    a.k_old, a.v_old, a.k_new, a.v_new, a.dtype = _p(k_old), _p(v_old), _p(k_new), _p(v_new), _dt(ref)
+    a.n_old = kv_old.shape[0] if kv_old is not None else 0
+    a.n_new = kv_new.shape[0] if kv_new is not None else 0
+    a.H, a.D, a.V, a.R, a.kv_rank = int(H), int(D), int(V), int(R), int(kv_rank)
+    _lib.check_seq(_lib.load_seq().cc_seq_latent_expand(C.byref(a), _stream()), "cc_seq_latent_expand")
+
+
+def head_gate(y, g):
+    """y [T, H, V] *= sigmoid(g[t, h]) (g: fp32 column range [T, H])."""
+    _need(("y", y, None))
+    ptr, ld = _cols(_f32("g", g))
+    T, H, V = y.shape
+    _lib.check_seq(_lib.load_seq().cc_seq_head_gate(_p(y), _dt(y), ptr, ld, T, H, V, _stream()), "cc_seq_head_gate")
+
+
+def head_gemv(w, x, sx, out, so, gate=None):
+    """out[h * so + n] = w[h, n, :] . x[h * sx : h * sx + K] (* sigmoid(gate[h])); one token."""
+    _need(("w", w, None), ("gate", gate, torch.float32))
+    H, N, K = w.shape
+    _lib.check_seq(_lib.load_seq().cc_seq_head_gemv(_p(w), _dt(w), x.data_ptr(), _dt(x), int(sx), out.data_ptr(), _dt(out), int(so),
+                                                    _p(gate), H, N, K, _stream()), "cc_seq_head_gemv")
+
+
+def wkv(r, k, v, wraw, w0, u, state, o, H, D):
+    _need(*[(n, t, torch.float32) for n, t in (("r", r), ("k", k), ("v", v), ("wraw", wraw), ("w0", w0), ("u", u),
+                                               ("state", state), ("o", o))])
+    a = _lib.CcSeqWkv()
+    a.r, a.k, a.v, a.wraw, a.w0, a.u, a.state, a.o = _p(r), _p(k), _p(v), _p(wraw), _p(w0), _p(u), _p(state), _p(o)
+    a.T, a.H, a.D = r.shape[0], int(H), int(D)
+    assert r.shape[1] == H * D and state.numel() == H * D * D
+    _lib.check_seq(_lib.load_seq().cc_seq_wkv(C.byref(a), _stream()), "cc_seq_wkv")
+
+
+def head_norm_gate(o, graw, nw, out, H, D, eps):
+    _need(("o", o, torch.float32), ("nw", nw, torch.float32), ("out", out, None))
+    ptr, ld = _cols(_f32("graw", graw))
+    _lib.check_seq(_lib.load_seq().cc_seq_head_norm_gate(_p(o), ptr, ld, _p(nw), _p(out), _dt(out), o.shape[0], int(H), int(D),
+                                                         float(eps), _stream()), "cc_seq_head_norm_gate")
+
+
+def moe_route(logits, correction, ids, wts, groups, keep, top):
+    _need(("correction", correction, torch.float32), ("ids", ids, torch.int32), ("wts", wts, torch.float32))
+    ptr, ld = _cols(_f32("logits", logits))
+    T, n = logits.shape
+    _lib.check_seq(_lib.load_seq().cc_seq_moe_route(ptr, ld, _p(correction), _p(ids), _p(wts), T, n, int(groups), int(keep), int(top),
+                                                    _stream()), "cc_seq_moe_route")
+
+
+def moe_group(ids, n_real, counts, slot, perm):
+    _need(("ids", ids, torch.int32), ("counts", counts, torch.int32), ("slot", slot, torch.int32), ("perm", perm, torch.int32))
+    _lib.check_seq(_lib.load_seq().cc_seq_moe_group(_p(ids), ids.numel(), ids.shape[-1], int(n_real), _p(counts), _p(slot), _p(perm),
+                                                    _stream()), "cc_seq_moe_group")
+
+
+def gather_rows(src, perm, dst, M):
+    _need(("src", src, None), ("perm", perm, torch.int32), ("dst", dst, src.dtype))
+    _lib.check_seq(_lib.load_seq().cc_seq_gather_rows(_p(src), _p(perm), _p(dst), _dt(src), int(M), src.shape[-1], _stream()),
+                   "cc_seq_gather_rows")
+
+
+def moe_expert_tokens(wgu, wd, h, ids, act, y, kind):
+    """Experts of a few tokens, no grouping: wgu [n, 2F, E], wd [n, E, F], h [T, E], ids [T, top] -> y fp32 [T * top, E]."""
+    _need(("wgu", wgu, None), ("wd", wd, wgu.dtype), ("h", h, wgu.dtype), ("ids", ids, torch.int32), ("act", act, wgu.dtype),
+          ("y", y, torch.float32))
+    n, F2, E = wgu.shape
+    T, top = ids.shape
+    _lib.check_seq(_lib.load_seq().cc_seq_moe_expert_tokens(_p(wgu), _p(wd), _p(h), _p(ids), _p(act), _p(y), _dt(wgu), T, top, n,
+                                                            F2 // 2, E, int(kind), _stream()), "cc_seq_moe_expert_tokens")
+
+
+def moe_combine(ids, wts, slot, y, h, shared, sg, out, n_real):
+    _need(("ids", ids, torch.int32), ("wts", wts, torch.float32), ("slot", slot, torch.int32), ("y", y, torch.float32),
+          ("h", h, torch.float32), ("shared", shared, torch.float32), ("out", out, torch.float32))
+    a = _lib.CcSeqMoeCombine()
+    a.ids, a.wts, a.slot, a.y, a.h, a.shared, a.out = _p(ids), _p(wts), _p(slot), _p(y), _p(h), _p(shared), _p(out)
+    a.sg, a.ld_sg = _cols(_f32("sg", sg))
+    a.T, a.top = ids.shape
+    a.E, a.n_real = out.shape[-1], int(n_real)
+    _lib.check_seq(_lib.load_seq().cc_seq_moe_combine(C.byref(a), _stream()), "cc_seq_moe_combine")
+
+
+def cache_append(k_new, v_new, k_cache, v_cache, pos, mask, cache_cts, input_pos):
+    """Rows k_new [T, G, Dk] / v_new [T, G, Dv] into slots (position mod L) of a cache, with pos / mask / cache_cts."""
+    _need(("k_new", k_new, k_cache.dtype), ("v_new", v_new, k_cache.dtype), ("k_cache", k_cache, None), ("v_cache", v_cache, k_cache.dtype),
+          ("pos", pos, torch.int32), ("mask", mask, torch.bool), ("cache_cts", cache_cts, torch.int32), ("input_pos", input_pos, torch.int32))
+    a = _lib.CcSeqAttn()
+    a.k_new, a.v_new, a.k_cache, a.v_cache = _p(k_new), _p(v_new), _p(k_cache), _p(v_cache)
+    a.pos, a.mask, a.cache_cts, a.input_pos = _p(pos), _p(mask), _p(cache_cts), _p(input_pos)
+    a.T, a.G, a.Dk = k_new.shape
+    a.Dv, a.L, a.H, a.cache_dtype = v_new.shape[-1], k_cache.shape[-2], k_new.shape[1], _dt(k_cache)
+    _lib.check_seq(_lib.load_seq().cc_seq_cache_append(C.byref(a), _stream()), "cc_seq_cache_append")
+
+
+def attention_rows(q, k_new, v_new, k_old, v_old, pos_old, input_pos, y, scale, window=0):
+    """Causal attention of T new tokens over n_old earlier rows and themselves, none of it through a cache object:
+    q fp32 [T, H, Dk], k_new [T, G, Dk], v_new [T, G, Dv]; k_old [G, n_old, Dk], v_old [G, n_old, Dv] with pos_old
+    int32 [n_old] = the position each old row holds (row j must hold position j); n_old may be 0 (pass None)."""
+    _need(("q", q, torch.float32), ("k_new", k_new, None), ("v_new", v_new, k_new.dtype), ("k_old", k_old, k_new.dtype),
+          ("v_old", v_old, k_new.dtype), ("pos_old", pos_old, torch.int32), ("input_pos", input_pos, torch.int32), ("y", y, None))
+    a = _lib.CcSeqAttn()
+    T, H, Dk = q.shape
+    G, Dv = k_new.shape[1], v_new.shape[-1]
+    assert k_new.shape == (T, G, Dk) and v_new.shape == (T, G, Dv) and y.shape == (T, H, Dv)
+    a.q, a.k_new, a.v_new, a.input_pos, a.y = _p(q), _p(k_new), _p(v_new), _p(input_pos), _p(y)
+    if k_old is None:      # no earlier rows: one slot that holds no position
+        a.k_cache, a.v_cache, a.pos, a.L = _p(k_new), _p(v_new), _p(_no_position(q.device)), 1
+    else:
+        assert k_old.shape[0] == G and v_old.shape[:2] == k_old.shape[:2] and pos_old.numel() == k_old.shape[1]
+        a.k_cache, a.v_cache, a.pos, a.L = _p(k_old), _p(v_old), _p(pos_old), k_old.shape[1]
+    a.T, a.H, a.G, a.Dk, a.Dv = T, H, G, Dk, Dv
+    a.window, a.sink_mode, a.cache_dtype, a.y_dtype, a.scale = int(window), _lib.SINK_NONE, _dt(k_new), _dt(y), float(scale)
+    _lib.check_seq(_lib.load_seq().cc_seq_attention(C.byref(a), _stream()), "cc_seq_attention")
+
+
+_NO_POSITION = {}
+
+
+def _no_position(device):
+    t = _NO_POSITION.get(device)
+    if t is None:
+        t = _NO_POSITION[device] = torch.full((1,), -1, dtype=torch.int32, device=device)
+    return t

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define CC_SEQ_ABI_VERSION 1
+#define CC_SEQ_ABI_VERSION 2
 
 #define CC_SEQ_OK                     0
 #define CC_SEQ_ERR_INVALID_ARG       -1
@@ -133,6 +133,146 @@ typedef struct CcSeqGemv {
 } CcSeqGemv;
 
 int cc_seq_gemv(const CcSeqGemv* g, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Second part (csrc/seq/mix_kernels.cu): layers that carry per-sequence state besides a key/value cache.
+ * Inputs named "fp32 [T, ld]" are usually column ranges of a fused projection's output: a pointer to the first
+ * column and the row stride in elements.
+ * ------------------------------------------------------------------------------------------------------------------ */
+
+/* activations of cc_seq_gated_unit and of the expert kernels */
+#define CC_ACT_NONE       0
+#define CC_ACT_GELU_TANH  1  /* 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) */
+#define CC_ACT_SILU       2  /* z sigmoid(z) */
+#define CC_ACT_TANH       3
+#define CC_ACT_SIGMOID    4
+
+/* x[t] = embed[tok[t]] * scale, fp32 [T, E] */
+int cc_seq_embed_rows(const int32_t* tokens, const void* embed, int32_t table_dtype, float* x, int32_t T, int32_t E,
+                      float scale, void* stream);
+
+/*
+ * Gated residual sum fused with the grouped RMS norm that reads it.  Per row t (row rows[i] when `rows` is given):
+ *   x[t] += a[t] * sigmoid(ga[t] + ba) + b[t] * sigmoid(gb[t] + bb)      (each term only if its pointer is set;
+ *                                                                         no gate when ga / gb is NULL)
+ *   h[i]  = x[t] split into `groups` equal consecutive parts, each divided by sqrt(mean(part^2) + eps), times w
+ * h (fp32) and h_act (act_dtype) are optional outputs, compact in i; w == NULL stops after the sum.
+ */
+typedef struct CcSeqGatedNorm {
+    float* x;                                   /* [*, E] fp32 residual stream, updated in place */
+    const float* a;  int64_t lda;  const float* ga;  int64_t ldga;  const float* ba;
+    const float* b;  int64_t ldb;  const float* gb;  int64_t ldgb;  const float* bb;
+    const float* w;                             /* [E] */
+    float* h;  void* h_act;  int32_t act_dtype;
+    const int64_t* rows;                        /* [T] or NULL */
+    int32_t T, E, groups;
+    float eps;
+} CcSeqGatedNorm;
+int cc_seq_gated_group_norm(const CcSeqGatedNorm* g, void* stream);
+
+/* Token shift: out[s][t] = h[t] + (h[t-1] - h[t]) * mu[s] for s < n, with h[-1] = state (fp32 [E]); afterwards
+ * state = h[T-1].  out [n, T, E] in out_dtype and / or outf fp32 [T, E] (mix 0 only). */
+int cc_seq_token_shift(const float* h, float* state, const float* mu, void* out, int32_t out_dtype, float* outf,
+                       int32_t T, int32_t E, int32_t n, void* stream);
+
+/* out[t, f] = act(in[t, off_gate + f]) * in[t, off_up + f]   (off_up < 0: no second factor); in fp32 [T, ld] */
+int cc_seq_gated_unit(const float* in, int64_t ld, int32_t off_gate, int32_t off_up, void* out, int32_t out_dtype,
+                      int32_t T, int32_t F, int32_t kind, void* stream);
+
+/*
+ * Rows of latent (low-rank) attention from the fused down-projection `in` fp32 [T, ld]:
+ *   cq[t]   = rms_norm(in[t, off_q : off_q + q_rank]) * wq                          (dtype, skipped when q_rank == 0)
+ *   krow[t] = [ rms_norm(in[t, off_kv : off_kv + kv_rank]) * wkv | rot(in[t, off_kv + kv_rank : + rot_dim]) ]
+ *   vrow[t] = the first kv_rank columns of krow[t] again                            (optional)
+ * rot() turns pairs (i, i + rot_dims/2) of the first rot_dims entries by the angle p * inv_freq[i], p = *input_pos + t.
+ */
+typedef struct CcSeqLatentPrep {
+    const float* in;  int64_t ld;
+    int32_t off_q, q_rank, off_kv, kv_rank, rot_dim, rot_dims;
+    const float* wq;  const float* wkv;  const float* inv_freq;
+    const int32_t* input_pos;
+    void* cq;  void* krow;  void* vrow;  int32_t dtype;
+    int32_t T;
+    float eps;
+} CcSeqLatentPrep;
+int cc_seq_latent_prepare(const CcSeqLatentPrep* a, void* stream);
+
+/* In place on q fp32 [T, ld] = H heads of head_w columns: the segment [off, off + seg) of every head is rotated
+ * (first `dims` entries, pairs (i, i + dims/2), angle p * inv_freq[i]).  With `tail`, the segment is also copied to
+ * tail[(t * H + h) * tail_ld + tail_off ...]. */
+int cc_seq_rope_heads(float* q, int64_t ld, const int32_t* input_pos, const float* inv_freq, int32_t T, int32_t H,
+                      int32_t head_w, int32_t off, int32_t seg, int32_t dims, float* tail, int64_t tail_ld,
+                      int32_t tail_off, void* stream);
+
+/*
+ * Per-head key / value rows from up-projected latents: kv_* fp32 [n, ld_kv] = [H*D key part | H*V values], lat_*
+ * [n, ld_lat] (dtype) = latent rows whose columns kv_rank .. kv_rank + R are the shared rotated key part.
+ * Old rows go to k_old [H, n_old, D + R] / v_old [H, n_old, V], new rows to k_new [n_new, H, D + R] / v_new [n_new, H, V].
+ */
+typedef struct CcSeqLatentExpand {
+    const float* kv_old;  const float* kv_new;  int64_t ld_kv;
+    const void* lat_old;  const void* lat_new;  int64_t ld_lat;
+    void* k_old;  void* v_old;  void* k_new;  void* v_new;
+    int32_t dtype, n_old, n_new, H, D, V, R, kv_rank;
+} CcSeqLatentExpand;
+int cc_seq_latent_expand(const CcSeqLatentExpand* a, void* stream);
+
+/* y [T, H, V] (dtype) *= sigmoid(g[t * ldg + h]) */
+int cc_seq_head_gate(void* y, int32_t dtype, const float* g, int64_t ldg, int32_t T, int32_t H, int32_t V, void* stream);
+
+/* One-token block-diagonal product: out[h * so + n] = W[h, n, :] . x[h * sx : h * sx + K]  (* sigmoid(gate[h])) */
+int cc_seq_head_gemv(const void* W, int32_t w_dtype, const void* x, int32_t x_dtype, int64_t sx, void* out,
+                     int32_t out_dtype, int64_t so, const float* gate, int32_t H, int32_t N, int32_t K, void* stream);
+
+/*
+ * Linear recurrence with a matrix state per head, fp32 throughout.  For t = 0 .. T-1, head h, with D-vectors
+ * r, k, v and the decay w_t = exp(-exp(wraw_t + w0)):
+ *   o_t[j]  = sum_i r_t[i] * (S[i][j] + u[i] * k_t[i] * v_t[j])
+ *   S[i][j] = w_t[i] * S[i][j] + k_t[i] * v_t[j]
+ * r, k, v, wraw, o: fp32 [T, H * D] contiguous; w0, u: [H * D]; state [H, D, D] is read and written.
+ */
+typedef struct CcSeqWkv {
+    const float* r;  const float* k;  const float* v;  const float* wraw;
+    const float* w0;  const float* u;
+    float* state;  float* o;
+    int32_t T, H, D;
+} CcSeqWkv;
+int cc_seq_wkv(const CcSeqWkv* a, void* stream);
+
+/* out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * nw[h, :] * silu(graw[t, h, :])   (graw fp32 [T, ldg]) */
+int cc_seq_head_norm_gate(const float* o, const float* graw, int64_t ldg, const float* nw, void* out, int32_t out_dtype,
+                          int32_t T, int32_t H, int32_t D, float eps, void* stream);
+
+/*
+ * Router of a mixture of experts over n outputs (real and identity experts alike), logits fp32 [T, ld]:
+ * scores s = softmax(logits); choice = s + correction; the outputs form `groups` equal groups of neighbours and only
+ * those of the `keep` groups with the largest maximal choice can be chosen; the `top` largest choices win;
+ * wts = s of the winners / (their sum + 1e-20).  ids int32 [T, top], wts fp32 [T, top].
+ */
+int cc_seq_moe_route(const float* logits, int64_t ld, const float* correction, int32_t* ids, float* wts, int32_t T,
+                     int32_t n, int32_t groups, int32_t keep, int32_t top, void* stream);
+
+/* Groups the M = T * top (token, choice) pairs by real expert (id < n_real): counts [n_real], slot [M] = row of the
+ * pair in expert order (-1 for an identity expert), perm [M] = token of each row. */
+int cc_seq_moe_group(const int32_t* ids, int32_t M, int32_t top, int32_t n_real, int32_t* counts, int32_t* slot,
+                     int32_t* perm, void* stream);
+int cc_seq_gather_rows(const void* src, const int32_t* perm, void* dst, int32_t dtype, int32_t M, int32_t E, void* stream);
+
+/* Experts for a few tokens without grouping: pair m = t * top + k with expert e = ids[m] < n_real:
+ * act[m] = act(Wgu[e, 0:F] h[t]) * (Wgu[e, F:2F] h[t]),  y[m] = Wd[e] act[m]  (fp32 [M, E]).  Weights, h and act in dtype. */
+int cc_seq_moe_expert_tokens(const void* Wgu, const void* Wd, const void* h, const int32_t* ids, void* act, float* y,
+                             int32_t dtype, int32_t T, int32_t top, int32_t n_real, int32_t F, int32_t E, int32_t kind,
+                             void* stream);
+
+/* out[t] = sum_k wts[t, k] * (ids[t, k] < n_real ? y[slot[t, k]] : h[t]) + sigmoid(sg[t * ld_sg]) * shared[t];
+ * slot == NULL means row t * top + k; shared may be NULL; sg == NULL means no gate on it. */
+typedef struct CcSeqMoeCombine {
+    const int32_t* ids;  const float* wts;  const int32_t* slot;
+    const float* y;  const float* h;  const float* shared;  const float* sg;  int64_t ld_sg;
+    float* out;
+    int32_t T, E, top, n_real;
+} CcSeqMoeCombine;
+int cc_seq_moe_combine(const CcSeqMoeCombine* a, void* stream);
 
 #ifdef __cplusplus
 }
