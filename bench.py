@@ -689,6 +689,58 @@ def _tidelorn_model(sz, device, dtype):
     return model.eval()
 
 
+DETATAR_SIZES = {
+    # the latent-attention layers keep the head count and a 128-wide head (96 unrotated + 32 rotated, values 128) of
+    # the same-named shape above; recurrent layers have width / 64 heads of 64; feed-forwards alternate between a
+    # dense one of the shape's size and experts (16, 4 chosen, + 2 identity, + a shared one) with about as many
+    # active rows
+    "1b": dict(q_rank=768, kv_rank=192, expert_ff=1536, shared_ff=2048),
+    "8b": dict(q_rank=1536, kv_rank=192, expert_ff=3072, shared_ff=2048),
+}
+
+
+def _detatar_config(sz, extra):
+    E = sz["width"]
+    latent = {"heads": sz["heads"], "dim": 96, "rot_dim": 32, "vdim": sz["head"], "q_rank": extra["q_rank"],
+              "kv_rank": extra["kv_rank"], "scale": 128 ** -0.5, "rot": {"base": 500000.0, "dims": 32}}
+    wkv = {"heads": E // 64, "dim": 64}
+    dense = {"kind": "dense", "ff": sz["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": extra["expert_ff"]}, "shared": {"ff": extra["shared_ff"]},
+           "router": {"experts": 16, "identity": 2, "top": 4, "groups": {"count": 6, "keep": 3}}}
+    layers = [{"type": "latent_attention" if i % 2 == 0 else "wkv", "mixer": latent if i % 2 == 0 else wkv,
+               "mlp": dense if i % 4 in (0, 3) else moe} for i in range(sz["layers"])]
+    return {"architecture": "Detatar", "vocab": sz["vocab"], "width": E, "norm": {"eps": 1e-5, "groups": 4},
+            "embedding": {"scale": E ** 0.5}, "layers": layers}
+
+
+def _detatar_model(sz, extra, device, dtype):
+    """A random-init Detatar of the given layer shape: latent-attention and recurrent layers alternate."""
+    from cold_compress_b200.detatar import DetatarTransformer, _zeros
+    with torch.device(device):
+        model = DetatarTransformer.from_config(_detatar_config(sz, extra), dtype)
+        for layer in model.layers:
+            m = layer.block.mixer
+            if layer.block.kind == "wkv" and m.w_w1.shape[0] == 0:     # the decay's low rank is a checkpoint shape
+                m.w_w1, m.w_w2 = _zeros(64, sz["width"], dtype=dtype), _zeros(m.heads * m.head_dim, 64, dtype=dtype)
+    gen = torch.Generator(device=device).manual_seed(0)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() >= 2 and "mu" not in name:
+                p.copy_(torch.empty(p.shape, device=device).normal_(0.0, 0.02, generator=gen))
+            elif name.endswith("weight") or name.endswith("norm_w") or "_norm" in name:
+                p.fill_(1.0)
+            elif "mu" in name:
+                p.fill_(0.5)
+            elif name.endswith("w0"):
+                p.fill_(-1.0)
+        for layer in model.layers:
+            if layer.block.kind == "latent_attention":
+                m = layer.block.mixer
+                H, D, C = m.heads, m.head_dim, m.kv_rank
+                m.w_uk_t.copy_(m.w_ukv[:H * D].reshape(H, D, C).transpose(1, 2))
+    return model.eval()
+
+
 def _llama_model(sz, device):
     from cold_compress_b200.model import ModelArgs, Transformer
     cfg = ModelArgs(block_size=sz["prompt"] + 1024, vocab_size=sz["vocab"], n_layer=sz["layers"], n_head=sz["heads"],
@@ -732,13 +784,15 @@ def run_design(args):
     names = [n for n in args.design.split(",") if n]
     flush = torch.zeros(64 << 20, dtype=torch.float32, device=device)
     rows = []
+    arms = ("detatar", "tidelorn") if args.design_model == "detatar" else ("tidelorn", "llama")
     for name in names:
         sz = DESIGN_SIZES[name]
         P = sz["prompt"]
         prompt = torch.randint(0, sz["vocab"], (P,), dtype=torch.int32, device=device, generator=torch.Generator(device=device).manual_seed(1))
         row = {"size": name, **sz}
-        for arm in ("tidelorn", "llama"):
-            model = _tidelorn_model(sz, device, torch.bfloat16) if arm == "tidelorn" else _llama_model(sz, device)
+        for arm in arms:
+            model = (_detatar_model(sz, DETATAR_SIZES[name], device, torch.bfloat16) if arm == "detatar" else
+                     _tidelorn_model(sz, device, torch.bfloat16) if arm == "tidelorn" else _llama_model(sz, device))
             ck = cache_kwargs(dict(slots=1.0, pattern="tile", strategy="full", compressor="recent_global"))
             ck["global_tokens"] = 0
             gu.setup_caches(model, SyntheticTokenizer(vocab_size=sz["vocab"]), device, P + 1024, ck)
@@ -771,6 +825,13 @@ def run_design(args):
                 torch.cuda.synchronize()
                 dms = a.elapsed_time(b) / args.steps
             wbytes = sum(p.numel() * p.element_size() for n, p in model.named_parameters() if p.dim() >= 2 and "tok_embeddings" not in n and "bigram" not in n)
+            if arm == "detatar":      # a token reads `top` experts of each mixture, not all of them, and one copy of W_uk
+                for layer in model.layers:
+                    f, m = layer.block.mlp, layer.block.mixer
+                    if hasattr(f, "w_gu"):
+                        wbytes -= (f.n_real - f.top) * (f.w_gu[0].numel() + f.w_d[0].numel()) * f.w_gu.element_size()
+                    if hasattr(m, "w_uk_t"):
+                        wbytes -= m.w_uk_t.numel() * m.w_uk_t.element_size()
             row[arm] = {"prefill_tokens_per_s": round(P / ms * 1e3, 1), "prefill_ms": round(ms, 3),
                         "decode_tokens_per_s": round(1e3 / dms, 1), "decode_ms": round(dms, 4),
                         "decode_weight_stream_frac_of_hbm": round(wbytes / (dms * 1e-3) / 1e9 / hbm, 3),
@@ -778,8 +839,12 @@ def run_design(args):
             del model, decoder
             torch.cuda.empty_cache()
         row["kernels"] = _design_kernels(sz, device, hbm)
+        if args.design_model == "detatar":
+            row["detatar_kernels"] = _detatar_kernels(sz, DETATAR_SIZES[name], device, hbm)
         rows.append(row)
-    print(json.dumps({"metric": "prefill and decode tokens/s, Tidelorn beside Llama (full cache) at equal layer shape",
+    metric = ("prefill and decode tokens/s, Detatar beside Tidelorn at equal layer shape" if args.design_model == "detatar" else
+              "prefill and decode tokens/s, Tidelorn beside Llama (full cache) at equal layer shape")
+    print(json.dumps({"metric": metric,
                       "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "steps": args.steps, "sizes": rows,
                       "peaks": {"hbm_gbs": hbm}}), flush=True)
 
@@ -824,6 +889,73 @@ def _design_kernels(sz, device, hbm):
 
 
 
+def _detatar_kernels(sz, extra, device, hbm):
+    """The Detatar kernels that have no counterpart in the other arm, alone at this shape: the matrix-state recurrence
+    over a whole prompt and for one token, the absorbed one-token attention over latent rows, and the chosen experts
+    of one token."""
+    from cold_compress_b200 import _lib, seq_ops
+    from cold_compress_b200.cache import get_cache_constructor
+    P, E = sz["prompt"], sz["width"]
+    H, D = E // 64, 64
+    gen = torch.Generator(device=device).manual_seed(3)
+    out = {}
+    r, k, v = (torch.randn(P, H * D, device=device, generator=gen) * 0.1 for _ in range(3))
+    wraw = torch.randn(P, H * D, device=device, generator=gen)
+    w0, u = torch.full((H * D,), -1.0, device=device), torch.zeros(H * D, device=device)
+    state = torch.zeros(H, D, D, device=device)
+    o = torch.empty(P, H * D, device=device)
+    ms = _time_events(lambda: seq_ops.wkv(r, k, v, wraw, w0, u, state, o, H, D), 2, 3)
+    out["recurrence_prompt"] = {"ms": round(ms, 3), "fp32_tflops": round(4.0 * P * H * D * D / ms / 1e9, 2),
+                                "gb_per_s": round(5.0 * P * H * D * 4 / ms / 1e6, 1)}
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(20):
+            seq_ops.wkv(r[:1], k[:1], v[:1], wraw[:1], w0, u, state, o[:1], H, D)
+    us = _time_events(graph.replay, 2, 5) * 1e3 / 20
+    nbytes = 2 * H * D * D * 4
+    out["recurrence_token"] = {"us": round(us, 2), "gb_per_s": round(nbytes / us / 1e3, 1), "frac_of_hbm": round(nbytes / us / 1e3 / hbm, 3)}
+    # absorbed attention: all query heads over one latent row per position
+    Hq, C, R = sz["heads"], extra["kv_rank"], 32
+    ctor, _ = get_cache_constructor("latent")
+    with torch.device(device):
+        cache = ctor(1, 1, C + R, torch.bfloat16, v_head_dim=C, max_cache_length=P + 8, max_seq_length=P + 8)
+    rows = torch.randn(P, 1, C + R, device=device, generator=gen).to(torch.bfloat16)
+    cache.sequence_append(rows, torch.zeros(1, dtype=torch.int32, device=device))
+    q = torch.randn(1, Hq, C + R, device=device, generator=gen)
+    y = torch.empty(1, Hq, C, device=device, dtype=torch.bfloat16)
+    ipd = torch.tensor([P], dtype=torch.int32, device=device)
+    step = lambda: cache.latent_step(q, rows[:1], ipd, y, 0.1)
+    step()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(20):
+            step()
+    us = _time_events(graph.replay, 2, 5) * 1e3 / 20
+    nbytes, flops = P * (C + R) * 2, 2.0 * P * Hq * (2 * C + R)
+    out["decode_attention_latent"] = {"us": round(us, 2), "launches": 2, "gb_per_s": round(nbytes / us / 1e3, 1),
+                                      "frac_of_hbm": round(nbytes / us / 1e3 / hbm, 3), "fp32_tflops": round(flops / us / 1e6, 2)}
+    # the chosen experts of one token
+    n, top, F = 16, 4, extra["expert_ff"]
+    wgu = (torch.randn(n, 2 * F, E, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+    wd = (torch.randn(n, E, F, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+    h = torch.randn(1, E, device=device, generator=gen).to(torch.bfloat16)
+    ids = torch.tensor([[1, 5, 9, 14]], dtype=torch.int32, device=device)
+    act = torch.empty(top, F, device=device, dtype=torch.bfloat16)
+    yy = torch.empty(top, E, device=device)
+    graph = torch.cuda.CUDAGraph()
+    seq_ops.moe_expert_tokens(wgu, wd, h, ids, act, yy, _lib.ACT_SILU)
+    torch.cuda.synchronize()
+    with torch.cuda.graph(graph):
+        for i in range(4):      # other experts each time: 4 x 4 of the 16, so that no weight comes from L2
+            seq_ops.moe_expert_tokens(wgu, wd, h, (ids + i) % n if i else ids, act, yy, _lib.ACT_SILU)
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=device)
+    us = _time_events(graph.replay, 2, 5, flush) * 1e3 / 4
+    nbytes = top * 3 * F * E * 2
+    out["experts_token"] = {"us": round(us, 2), "gb_per_s": round(nbytes / us / 1e3, 1), "frac_of_hbm": round(nbytes / us / 1e3 / hbm, 3)}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -836,6 +968,9 @@ def main():
     ap.add_argument("--design", default="", metavar="SIZES",
                     help="instead of the headline workload: Tidelorn beside the Llama-family model at equal layer shape, "
                          "comma-separated sizes of " + "/".join(DESIGN_SIZES))
+    ap.add_argument("--design-model", default="tidelorn", choices=["tidelorn", "detatar"],
+                    help="with --design: which design is measured (tidelorn: beside the Llama-family model; detatar: beside "
+                         "Tidelorn; sizes " + "/".join(DETATAR_SIZES) + ")")
     args = ap.parse_args()
     if args.design:
         return run_design(args)

@@ -179,7 +179,19 @@ class CcSeqGatedNorm(C.Structure):
     _fields_ = [("x", _vp), ("a", _vp), ("lda", _i64), ("ga", _vp), ("ldga", _i64), ("ba", _vp),
                 ("b", _vp), ("ldb", _i64), ("gb", _vp), ("ldgb", _i64), ("bb", _vp), ("w", _vp),
                 ("h", _vp), ("h_act", _vp), ("act_dtype", _i32), ("rows", _vp), ("T", _i32), ("E", _i32), ("groups", _i32),
-                ("eps", _f32)]
+                ("eps", _f32), ("shift_state", _vp), ("shift_mu", _vp), ("hs_act", _vp), ("mix_state", _vp), ("mix_mu", _vp),
+                ("mixes", _vp), ("n_mix", _i32)]
+
+
+GEMV_MAX_JOBS = 6
+
+
+class CcSeqGemvJob(C.Structure):
+    _fields_ = [("x", _vp), ("W", _vp), ("out", _vp)] + [(n, _i32) for n in ("x_dtype", "kind", "off_gate", "off_up", "N", "K")]
+
+
+class CcSeqGemvMulti(C.Structure):
+    _fields_ = [("job", CcSeqGemvJob * GEMV_MAX_JOBS), ("n_jobs", _i32), ("w_dtype", _i32)]
 
 
 class CcSeqLatentPrep(C.Structure):
@@ -191,6 +203,12 @@ class CcSeqLatentExpand(C.Structure):
     _fields_ = [("kv_old", _vp), ("kv_new", _vp), ("ld_kv", _i64), ("lat_old", _vp), ("lat_new", _vp), ("ld_lat", _i64)] + [
         (n, _vp) for n in ("k_old", "v_old", "k_new", "v_new")] + [
         (n, _i32) for n in ("dtype", "n_old", "n_new", "H", "D", "V", "R", "kv_rank")]
+
+
+class CcSeqLatentDecode(C.Structure):
+    _fields_ = [(n, _vp) for n in ("q", "k_new", "k_cache", "pos", "mask", "cache_cts", "input_pos", "y")] + [
+        (n, _i32) for n in ("H", "Dk", "C", "L", "cache_dtype", "y_dtype")] + [("scale", _f32), ("append", _i32),
+                                                                               ("workspace", _vp), ("workspace_bytes", C.c_uint64)]
 
 
 class CcSeqWkv(C.Structure):
@@ -210,6 +228,9 @@ SEQ_EXPORTS.update({
     "cc_seq_latent_prepare": (C.c_int, [C.POINTER(CcSeqLatentPrep), _vp]),
     "cc_seq_rope_heads": (C.c_int, [_vp, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _i32, _vp]),
     "cc_seq_latent_expand": (C.c_int, [C.POINTER(CcSeqLatentExpand), _vp]),
+    "cc_seq_latent_decode": (C.c_int, [C.POINTER(CcSeqLatentDecode), _vp]),
+    "cc_seq_latent_decode_workspace": (C.c_uint64, [_i32, _i32, _i32]),
+    "cc_seq_gemv_multi": (C.c_int, [C.POINTER(CcSeqGemvMulti), _vp]),
     "cc_seq_head_gate": (C.c_int, [_vp, _i32, _vp, _i64, _i32, _i32, _i32, _vp]),
     "cc_seq_head_gemv": (C.c_int, [_vp, _i32, _vp, _i32, _i64, _vp, _i32, _i64, _vp, _i32, _i32, _i32, _vp]),
     "cc_seq_wkv": (C.c_int, [C.POINTER(CcSeqWkv), _vp]),

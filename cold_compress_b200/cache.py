@@ -247,6 +247,16 @@ class KVCache(nn.Module):
                 int(window), int(sink_mode), float(scale))
         if T == 1 and q.shape[1] <= 16 * self.n_heads:   # the one-token kernel holds up to 16 query heads per KV head
             seq_ops.seq_attention(*args, seq_ops.ATTN_DECODE_APPEND, self._sequence_workspace(q.shape[1], window))
+        elif T == 1 and self.n_heads == 1:
+            # many query heads over one shared row per position (latent rows): 16 heads per launch; every launch takes
+            # the new key from k_new, the last one also appends it
+            H = q.shape[1]
+            for h0 in range(0, H, 16):
+                h1 = min(H, h0 + 16)
+                part = (q[:, h0:h1], k_new, v_new, self.k_cache, self.v_cache, self.pos, self.mask, self.cache_cts, input_pos,
+                        y[:, h0:h1], None if sink is None else sink[h0:h1], int(window), int(sink_mode), float(scale))
+                seq_ops.seq_attention(*part, seq_ops.ATTN_DECODE_APPEND if h1 == H else seq_ops.ATTN_DECODE,
+                                      self._sequence_workspace(16, window))
         else:
             seq_ops.seq_attention(*args, seq_ops.ATTN_CHUNK, None)
             seq_ops.seq_attention(*args, seq_ops.ATTN_APPEND_ONLY, None)
@@ -773,23 +783,41 @@ class KVCacheAnalysis(KVCacheFull):
 
 class KVCacheLatent(KVCacheFull):
     """The cache of a latent (low-rank) attention layer: one row per position, shared by all query heads, holding the
-    normalised key/value latent followed by the rotated key part (`k_cache` [1, 1, L, rank + rot]); `v_cache`
-    [1, 1, L, rank] holds the latent again as the value row of the absorbed one-token step.  Nothing is ever evicted
-    (slot = position), so it serves position-addressed steps like the full cache."""
+    normalised key/value latent followed by the rotated key part (`k_cache` [1, 1, L, rank + rot]).  There are no
+    value rows: a row's first `rank` columns are its value in the absorbed one-token step, and prompt portions
+    up-project the rows they need.  Nothing is ever evicted (slot = position)."""
 
     def __init__(self, max_batch_size, n_heads, head_dim, dtype=torch.bfloat16, **kwargs):
         if n_heads != 1:
             raise ValueError("a latent cache has one row per position for all heads")
         super().__init__(max_batch_size, n_heads, head_dim, dtype, **kwargs)
+        self.register_buffer("v_cache", torch.zeros((max_batch_size, 1, 0, 0), dtype=dtype))
 
     def latent_rows(self, n):
         """[n, rank + rot] view of the rows of positions 0 .. n-1."""
         return self.k_cache[0, 0, :n]
 
-    def sequence_append(self, k_new, v_new, input_pos):
-        """Appends T rows at positions input_pos[0] ... (prompt portions attend over expanded rows, then store the latents)."""
+    def sequence_step(self, *args, **kwargs):
+        raise _lib.CcError("a latent cache is read through latent_step (one token) or latent_rows (prompt portions)")
+
+    def sequence_append(self, k_new, input_pos):
+        """Stores T rows [T, 1, rank + rot] at positions input_pos[0] ... (a prompt portion, after it has attended)."""
         from . import seq_ops
-        seq_ops.cache_append(k_new, v_new, self.k_cache, self.v_cache, self.pos, self.mask, self.cache_cts, input_pos)
+        seq_ops.cache_append(k_new, None, self.k_cache, None, self.pos, self.mask, self.cache_cts, input_pos)
+
+    def latent_step(self, q, k_new, input_pos, y, scale):
+        """One token: q fp32 [1, H, rank + rot] over the cached rows and k_new [1, 1, rank + rot], which is then stored;
+        y [1, H, rank].  Two launches, positions read on the device (capturable in a graph)."""
+        from . import seq_ops
+        H, C = q.shape[-2], y.shape[-1]
+        key = ("latent", H, C, self.k_cache.device)
+        ws = self._out.get("latent_ws")
+        if ws is None or ws[0] != key:
+            nbytes = seq_ops.latent_decode_workspace_bytes(H, C, self.max_cache_length)
+            ws = (key, torch.empty((nbytes + 3) // 4, dtype=torch.float32, device=self.k_cache.device))
+            self._out["latent_ws"] = ws
+        seq_ops.latent_decode(q, k_new, self.k_cache, self.pos, self.mask, self.cache_cts, input_pos, y, scale, ws[1])
+        return y
 
 
 class RecurrentState(nn.Module):

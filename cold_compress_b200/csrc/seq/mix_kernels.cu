@@ -130,6 +130,16 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(const CcSeqGatedN
             const float h = row[c] * rinv * g.w[c];
             if (g.h != nullptr) g.h[(size_t)i * E + c] = h;
             if (g.h_act != nullptr) stf((ST*)g.h_act, (size_t)i * E + c, h);
+            if (g.shift_state != nullptr) {      // one token: its shifted copies in the same pass (thread c owns element c)
+                const float hs = h + (g.shift_state[c] - h) * g.shift_mu[c];
+                g.shift_state[c] = h;
+                if (g.hs_act != nullptr) stf((ST*)g.hs_act, c, hs);
+                if (g.n_mix > 0) {
+                    const float prev = g.mix_state[c];
+                    for (int m = 0; m < g.n_mix; ++m) stf((ST*)g.mixes, (size_t)m * E + c, hs + (prev - hs) * g.mix_mu[(size_t)m * E + c]);
+                    g.mix_state[c] = hs;
+                }
+            }
         }
     }
 }
@@ -285,56 +295,88 @@ __global__ void __launch_bounds__(256) head_gemv_kernel(const WT* __restrict__ W
 // channels of one head; thread (part, j) keeps WKV_CH rows of column j in registers.  Tokens are staged WKV_TB at a
 // time; the parts' partial outputs meet in shared memory after each batch, summed in part order, so the arithmetic of
 // a token does not depend on how the sequence was cut into launches.
-constexpr int WKV_J = 32, WKV_CH = 16, WKV_TB = 16;
+constexpr int WKV_J = 32, WKV_CH = 16, WKV_TB = 32;
 
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// Shared memory: two buffers of [r | k | w | v] for WKV_TB tokens (the next batch is copied in asynchronously while
+// this one is computed; rows are padded to a multiple of 4 floats so that a thread reads its 16 key channels with
+// 16-byte loads), then the parts' partial outputs.
 __global__ void wkv_kernel(const CcSeqWkv a) {
-    extern __shared__ float sm[];
-    const int D = a.D, P = (D + WKV_CH - 1) / WKV_CH;
-    float* rs = sm;                       // [TB][D]
-    float* ks = rs + WKV_TB * D;
-    float* ws = ks + WKV_TB * D;
-    float* vs = ws + WKV_TB * D;          // [TB][J]
-    float* us = vs + WKV_TB * WKV_J;      // [D]
-    float* part = us + D;                 // [TB][P][J]
+    extern __shared__ float4 smw4[];
+    float* sm = reinterpret_cast<float*>(smw4);
+    const int D = a.D, P = (D + WKV_CH - 1) / WKV_CH, Dp = P * WKV_CH;
+    const int buf_floats = WKV_TB * (3 * Dp + WKV_J);
+    float* part = sm + 2 * buf_floats;    // [TB][P][J]
     const int h = blockIdx.x, j0 = blockIdx.y * WKV_J;
     const int tid = threadIdx.x, nth = blockDim.x, jl = tid % WKV_J, p = tid / WKV_J, j = j0 + jl;
     const int i0 = p * WKV_CH;
     const size_t HD = (size_t)a.H * D;
     float* S = a.state + (size_t)h * D * D;
-    float st[WKV_CH];
+    float st[WKV_CH], u[WKV_CH];
 #pragma unroll
-    for (int c = 0; c < WKV_CH; ++c) st[c] = (i0 + c < D && j < D) ? S[(size_t)(i0 + c) * D + j] : 0.f;
-    for (int i = tid; i < D; i += nth) us[i] = a.u[(size_t)h * D + i];
-    for (int tb = 0; tb < a.T; tb += WKV_TB) {
+    for (int c = 0; c < WKV_CH; ++c) {
+        const bool in = i0 + c < D && j < D;
+        st[c] = in ? S[(size_t)(i0 + c) * D + j] : 0.f;
+        u[c] = i0 + c < D ? a.u[(size_t)h * D + i0 + c] : 0.f;
+    }
+    for (int idx = tid; idx < 2 * buf_floats; idx += nth) sm[idx] = 0.f;    // padding channels stay zero
+    __syncthreads();
+    auto fetch = [&](int tb, float* buf) {
         const int nt = min(WKV_TB, a.T - tb);
-        __syncthreads();
         for (int idx = tid; idx < nt * D; idx += nth) {
             const int t = idx / D, i = idx - t * D;
             const size_t src = (size_t)(tb + t) * HD + (size_t)h * D + i;
-            rs[idx] = a.r[src];
-            ks[idx] = a.k[src];
-            ws[idx] = expf(-expf(a.wraw[src] + a.w0[(size_t)h * D + i]));
+            cp_async4(buf + t * Dp + i, a.r + src);
+            cp_async4(buf + WKV_TB * Dp + t * Dp + i, a.k + src);
+            cp_async4(buf + 2 * WKV_TB * Dp + t * Dp + i, a.wraw + src);
         }
         for (int idx = tid; idx < nt * WKV_J; idx += nth) {
             const int t = idx / WKV_J, c = idx - t * WKV_J;
-            vs[idx] = j0 + c < D ? a.v[(size_t)(tb + t) * HD + (size_t)h * D + j0 + c] : 0.f;
+            if (j0 + c < D) cp_async4(buf + 3 * WKV_TB * Dp + idx, a.v + (size_t)(tb + t) * HD + (size_t)h * D + j0 + c);
+        }
+        cp_async_commit();
+    };
+    fetch(0, sm);
+    int cur = 0;
+    for (int tb = 0; tb < a.T; tb += WKV_TB, cur ^= 1) {
+        float* buf = sm + cur * buf_floats;
+        const int nt = min(WKV_TB, a.T - tb);
+        if (tb + WKV_TB < a.T) { fetch(tb + WKV_TB, sm + (cur ^ 1) * buf_floats); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
+        __syncthreads();
+        float* ws = buf + 2 * WKV_TB * Dp;
+        for (int idx = tid; idx < nt * D; idx += nth) {      // decay from its raw form, in place
+            const int t = idx / D, i = idx - t * D;
+            ws[t * Dp + i] = expf(-expf(ws[t * Dp + i] + a.w0[(size_t)h * D + i]));
         }
         __syncthreads();
+        const float* vs = buf + 3 * WKV_TB * Dp;
         for (int t = 0; t < nt; ++t) {
             const float v = vs[t * WKV_J + jl];
-            const float* r = rs + t * D + i0;
-            const float* k = ks + t * D + i0;
-            const float* w = ws + t * D + i0;
-            float acc = 0.f;
+            const float4* r4 = reinterpret_cast<const float4*>(buf + t * Dp + i0);
+            const float4* k4 = reinterpret_cast<const float4*>(buf + WKV_TB * Dp + t * Dp + i0);
+            const float4* w4 = reinterpret_cast<const float4*>(ws + t * Dp + i0);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < WKV_CH; ++c) {
-                if (i0 + c < D) {
-                    const float kv = k[c] * v;
-                    acc = fmaf(r[c], fmaf(us[i0 + c], kv, st[c]), acc);
-                    st[c] = fmaf(w[c], st[c], kv);
+            for (int c4 = 0; c4 < WKV_CH / 4; ++c4) {
+                const float4 rv = r4[c4], kv4 = k4[c4], wv = w4[c4];
+                const float rr[4] = {rv.x, rv.y, rv.z, rv.w}, kk[4] = {kv4.x, kv4.y, kv4.z, kv4.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int c = 4 * c4 + e;
+                    const float kv = kk[e] * v;
+                    acc[e] = fmaf(rr[e], fmaf(u[c], kv, st[c]), acc[e]);
+                    st[c] = fmaf(ww[e], st[c], kv);
                 }
             }
-            part[(t * P + p) * WKV_J + jl] = acc;
+            part[(t * P + p) * WKV_J + jl] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
         }
         __syncthreads();
         for (int idx = tid; idx < nt * WKV_J; idx += nth) {
@@ -530,6 +572,279 @@ __global__ void moe_combine_kernel(const CcSeqMoeCombine a) {
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------ absorbed latent attention
+// One token, all query heads over one shared row per position ([latent | rotated key part], Dk columns), whose first
+// C columns are also the value row: a key tile is staged once and serves scores and values.  Grid = (runs of keys,
+// groups of LD_HG heads); a warp owns one head, a lane one key of the 32-key tile (scores) and value columns
+// lane, lane + 32, ... (weighted sum).  Keys are addressed by position (slot = position mod L, counted only if the
+// slot records that position); the newest key comes from k_new.  Every run leaves (max, sum, weighted values) per
+// head in the workspace; latent_combine_kernel merges the live runs in run order and appends the new row.
+constexpr int LD_TK = 32, LD_HG = 8, LD_THREADS = 256;
+
+__host__ __device__ inline int ld_stride(int width) {   // floats; a multiple of 4 whose quarter is odd
+    const int w4 = (width + 3) / 4;
+    return 4 * (w4 | 1);
+}
+__host__ __device__ inline int ld_keys_per_run(int L) { return LD_TK * ((L + LD_TK * 128 - 1) / (LD_TK * 128)); }   // at most 128 runs
+
+template <typename CT, int NC>
+__global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(const CcSeqLatentDecode a) {
+    extern __shared__ float4 sml4[];
+    float* sm = reinterpret_cast<float*>(sml4);
+    const int Dk = a.Dk, C = a.C, Dkp = ld_stride(Dk), Dk4 = (Dk + 3) / 4;
+    float* Qs = sm;                         // [LD_HG][Dkp]
+    float* Ks = Qs + LD_HG * Dkp;           // [LD_TK][Dkp]
+    float* Ps = Ks + LD_TK * Dkp;           // [LD_HG][LD_TK]
+    int* src = (int*)(Ps + LD_HG * LD_TK);  // [LD_TK] slot, -1 = not a key, -2 = the new row
+    const int p = a.input_pos[0], kpr = ld_keys_per_run(a.L);
+    const int j_begin = blockIdx.x * kpr;
+    if (j_begin > p) return;
+    const int j_end = min(p, j_begin + kpr - 1);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h0 = blockIdx.y * LD_HG, nh = min(LD_HG, a.H - h0);
+    const CT* kc = (const CT*)a.k_cache;
+    const CT* kn = (const CT*)a.k_new;
+    for (int idx = tid; idx < LD_HG * Dkp; idx += LD_THREADS) {
+        const int h = idx / Dkp, d = idx - h * Dkp;
+        Qs[idx] = (h < nh && d < Dk) ? a.q[(size_t)(h0 + h) * Dk + d] : 0.f;
+    }
+    for (int idx = tid; idx < LD_TK * (Dkp - Dk); idx += LD_THREADS) {   // padding columns stay zero
+        const int r = idx / (Dkp - Dk), d = Dk + idx - r * (Dkp - Dk);
+        Ks[r * Dkp + d] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f, o[NC];
+#pragma unroll
+    for (int i = 0; i < NC; ++i) o[i] = 0.f;
+    constexpr int VEC = 16 / (int)sizeof(CT);
+    const bool vec = Dk % VEC == 0;
+    for (int jt = j_begin; jt <= j_end; jt += LD_TK) {
+        __syncthreads();
+        if (tid < LD_TK) {
+            const int j = jt + tid;
+            int sl = -1;
+            if (j <= j_end) {
+                if (j == p) sl = -2;
+                else { const int slot = j % a.L; sl = a.pos[slot] == j ? slot : -1; }
+            }
+            src[tid] = sl;
+        }
+        __syncthreads();
+        if (vec) {
+            const int per_row = Dk / VEC;
+            for (int idx = tid; idx < LD_TK * per_row; idx += LD_THREADS) {
+                const int r = idx / per_row, c = (idx - r * per_row) * VEC, sl = src[r];
+                float* d = Ks + r * Dkp + c;
+                if (sl == -1) {
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) d[e] = 0.f;
+                } else {
+                    const CT* row = sl == -2 ? kn : kc + (size_t)sl * Dk;
+                    const uint4 u = __ldg(reinterpret_cast<const uint4*>(row + c));
+                    const CT* e8 = reinterpret_cast<const CT*>(&u);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) d[e] = ldf(e8, e);
+                }
+            }
+        } else {
+            for (int idx = tid; idx < LD_TK * Dk; idx += LD_THREADS) {
+                const int r = idx / Dk, c = idx - r * Dk, sl = src[r];
+                Ks[r * Dkp + c] = sl == -1 ? 0.f : ldf(sl == -2 ? kn : kc + (size_t)sl * Dk, c);
+            }
+        }
+        __syncthreads();
+        if (warp < nh) {
+            const float4* q4 = reinterpret_cast<const float4*>(Qs + warp * Dkp);
+            const float4* k4 = reinterpret_cast<const float4*>(Ks + lane * Dkp);
+            float s = 0.f;
+#pragma unroll 4
+            for (int d = 0; d < Dk4; ++d) {
+                const float4 qv = q4[d], kv = k4[d];
+                s = fmaf(qv.x, kv.x, s); s = fmaf(qv.y, kv.y, s); s = fmaf(qv.z, kv.z, s); s = fmaf(qv.w, kv.w, s);
+            }
+            const bool valid = src[lane] != -1;
+            s = valid ? s * a.scale : -INFINITY;
+            float mt = s;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, off));
+            const float m_new = fmaxf(m, mt);
+            if (m_new != -INFINITY) {
+                const float corr = m == -INFINITY ? 0.f : expf(m - m_new);
+                const float pj = valid ? expf(s - m_new) : 0.f;
+                l = l * corr + warp_sum(pj);
+                Ps[warp * LD_TK + lane] = pj;
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < NC; ++i) o[i] *= corr;
+                for (int j = 0; j < LD_TK; ++j) {
+                    const float pw = Ps[warp * LD_TK + j];
+                    const float* kr = Ks + j * Dkp + lane;
+#pragma unroll
+                    for (int i = 0; i < NC; ++i)
+                        if (lane + 32 * i < C) o[i] = fmaf(pw, kr[32 * i], o[i]);
+                }
+                m = m_new;
+                __syncwarp();
+            }
+        }
+    }
+    if (warp < nh) {
+        float* w = (float*)a.workspace + ((size_t)blockIdx.x * a.H + h0 + warp) * (2 + C);
+        if (lane == 0) { w[0] = m; w[1] = l; }
+#pragma unroll
+        for (int i = 0; i < NC; ++i)
+            if (lane + 32 * i < C) w[2 + lane + 32 * i] = o[i];
+    }
+}
+
+// One CTA per head: the global maximum over the live runs, then warp w sums runs w, w + 8, ... for value columns
+// lane, lane + 32, ... and the eight partial sums meet in shared memory in warp order.
+constexpr int LC_WARPS = 8;
+template <typename CT, typename YT, int NC>
+__global__ void __launch_bounds__(LC_WARPS * 32) latent_combine_kernel(const CcSeqLatentDecode a) {
+    extern __shared__ float smc[];          // [LC_WARPS][C + 1]
+    __shared__ float red[LC_WARPS];
+    const int h = blockIdx.x, C = a.C, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int p = a.input_pos[0], runs = p / ld_keys_per_run(a.L) + 1;
+    const float* ws = (const float*)a.workspace;
+    const size_t stride = (size_t)a.H * (2 + C);
+    const float* mine = ws + (size_t)h * (2 + C);
+    float mx = -INFINITY;
+    for (int r = tid; r < runs; r += LC_WARPS * 32) mx = fmaxf(mx, mine[r * stride]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = red[0];
+#pragma unroll
+    for (int i = 1; i < LC_WARPS; ++i) mx = fmaxf(mx, red[i]);
+    float l = 0.f, acc[NC];
+#pragma unroll
+    for (int i = 0; i < NC; ++i) acc[i] = 0.f;
+    for (int r = warp; r < runs; r += LC_WARPS) {
+        const float* w = mine + r * stride;
+        const float mr = w[0];
+        const float wt = mr == -INFINITY ? 0.f : expf(mr - mx);
+        l = fmaf(wt, w[1], l);
+#pragma unroll
+        for (int i = 0; i < NC; ++i)
+            if (lane + 32 * i < C) acc[i] = fmaf(wt, w[2 + lane + 32 * i], acc[i]);
+    }
+    float* out = smc + warp * (C + 1);
+    if (lane == 0) out[C] = l;
+#pragma unroll
+    for (int i = 0; i < NC; ++i)
+        if (lane + 32 * i < C) out[lane + 32 * i] = acc[i];
+    __syncthreads();
+    float lt = 0.f;
+    for (int i = 0; i < LC_WARPS; ++i) lt += smc[i * (C + 1) + C];
+    for (int c = tid; c < C; c += LC_WARPS * 32) {
+        float v = 0.f;
+        for (int i = 0; i < LC_WARPS; ++i) v += smc[i * (C + 1) + c];
+        stf((YT*)a.y, (size_t)h * C + c, v / lt);
+    }
+    if (h == 0 && a.append) {   // the tile kernel took the newest key from k_new; nothing reads the cache here
+        const int slot = p % a.L;
+        CT* kc = (CT*)a.k_cache;
+        const CT* kn = (const CT*)a.k_new;
+        for (int d = tid; d < a.Dk; d += LC_WARPS * 32) kc[(size_t)slot * a.Dk + d] = kn[d];
+        if (tid == 0) {
+            if (a.mask != nullptr) a.mask[slot] = 1;
+            const int old = a.pos[slot];
+            a.pos[slot] = p;
+            if (old < 0 && a.cache_cts != nullptr) atomicAdd(a.cache_cts, 1);
+        }
+    }
+}
+
+template <typename CT, typename YT, int NC>
+static int launch_latent_decode(const CcSeqLatentDecode* a, cudaStream_t st) {
+    const int Dkp = ld_stride(a->Dk);
+    const size_t smem = sizeof(float) * ((size_t)(LD_HG + LD_TK) * Dkp + LD_HG * LD_TK) + sizeof(int) * LD_TK;
+    auto kern = latent_decode_kernel<CT, NC>;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        configured = smem;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return cuda_check("latent_decode: shared memory");
+    }
+    const int kpr = ld_keys_per_run(a->L);
+    dim3 grid((a->L + kpr - 1) / kpr, (a->H + LD_HG - 1) / LD_HG);
+    kern<<<grid, LD_THREADS, smem, st>>>(*a);
+    latent_combine_kernel<CT, YT, NC><<<a->H, LC_WARPS * 32, sizeof(float) * LC_WARPS * (a->C + 1), st>>>(*a);
+    return cuda_check("latent_decode kernels");
+}
+
+template <typename CT, typename YT>
+static int dispatch_latent_decode(const CcSeqLatentDecode* a, cudaStream_t st) {
+    const int nc = (a->C + 31) / 32;
+    if (nc <= 2) return launch_latent_decode<CT, YT, 2>(a, st);
+    if (nc <= 4) return launch_latent_decode<CT, YT, 4>(a, st);
+    if (nc <= 8) return launch_latent_decode<CT, YT, 8>(a, st);
+    if (nc <= 16) return launch_latent_decode<CT, YT, 16>(a, st);
+    if (nc <= 32) return launch_latent_decode<CT, YT, 32>(a, st);
+    return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "latent_decode: value rows wider than 1024");
+}
+
+// ------------------------------------------------------------------------------------------------ one-token products
+// Several independent matrix-vector products in one launch: job j is out_j = W_j xin_j with xin_j either the given
+// vector or, read from an fp32 row, act(src[off_gate + k]) * src[off_up + k] (the input side of a gated unit, or an
+// activation alone when off_up < 0).  The input is staged in shared memory rounded to the weights' type, as the
+// prompt path rounds what it hands to a product.  8 rows per CTA, a warp per row, 16-byte weight loads.
+__device__ __forceinline__ float round_to(float v, const float*) { return v; }
+__device__ __forceinline__ float round_to(float v, const bf16*) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+template <typename WT>
+__global__ void __launch_bounds__(256) gemv_multi_kernel(const CcSeqGemvMulti g) {
+    extern __shared__ float4 smg4[];
+    float* xs = reinterpret_cast<float*>(smg4);
+    int j = 0, first = 0;
+    while (j + 1 < g.n_jobs && (int)blockIdx.x >= first + (g.job[j].N + 7) / 8) { first += (g.job[j].N + 7) / 8; ++j; }
+    const CcSeqGemvJob& jb = g.job[j];
+    const int K = jb.K, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const WT* W = (const WT*)jb.W;
+    if (jb.kind != CC_ACT_NONE || jb.off_up >= 0) {
+        const float* src = (const float*)jb.x;
+        for (int k = tid; k < K; k += 256) {
+            float v = unit_act(src[jb.off_gate + k], jb.kind);
+            if (jb.off_up >= 0) v *= src[jb.off_up + k];
+            xs[k] = round_to(v, W);
+        }
+    } else if (jb.x_dtype == CC_DT_F32) {
+        for (int k = tid; k < K; k += 256) xs[k] = round_to(((const float*)jb.x)[k], W);
+    } else {
+        for (int k = tid; k < K; k += 256) xs[k] = __bfloat162float(((const bf16*)jb.x)[k]);
+    }
+    __syncthreads();
+    const int n = ((int)blockIdx.x - first) * 8 + warp;
+    if (n >= jb.N) return;
+    const WT* w = W + (size_t)n * K;
+    constexpr int VEC = 16 / (int)sizeof(WT);
+    float acc = 0.f;
+    if (K % VEC == 0) {
+        const uint4* w16 = reinterpret_cast<const uint4*>(w);
+        const int nv = K / VEC;
+#pragma unroll 4
+        for (int i = lane; i < nv; i += 32) {
+            const uint4 u = __ldg(w16 + i);
+            const WT* e = reinterpret_cast<const WT*>(&u);
+            const float4* x4 = reinterpret_cast<const float4*>(xs + i * VEC);
+#pragma unroll
+            for (int q = 0; q < VEC / 4; ++q) {
+                const float4 xv = x4[q];
+                acc = fmaf(ldf(e, 4 * q + 0), xv.x, acc);
+                acc = fmaf(ldf(e, 4 * q + 1), xv.y, acc);
+                acc = fmaf(ldf(e, 4 * q + 2), xv.z, acc);
+                acc = fmaf(ldf(e, 4 * q + 3), xv.w, acc);
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(ldf(w, k), xs[k], acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) ((float*)jb.out)[n] = acc;
+}
+
 static int blocks_for(size_t total, int threads) {
     size_t b = (total + threads - 1) / threads;
     return (int)(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
@@ -561,6 +876,8 @@ int cc_seq_embed_rows(const int32_t* tokens, const void* embed, int32_t table_dt
 int cc_seq_gated_group_norm(const CcSeqGatedNorm* g, void* stream) {
     if (!g || !g->x || g->T < 1 || g->E < 1 || g->groups < 1 || g->E % g->groups)
         return fail(CC_SEQ_ERR_INVALID_ARG, "gated_group_norm: bad argument");
+    if (g->shift_state && (g->T != 1 || g->rows || !g->w || !g->shift_mu || (g->n_mix > 0 && (!g->mix_state || !g->mix_mu || !g->mixes))))
+        return fail(CC_SEQ_ERR_INVALID_ARG, "gated_group_norm: the fused token shift serves one token");
     const size_t smem = sizeof(float) * (size_t)g->E;
     if (smem > 200 * 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "gated_group_norm: rows longer than 51200");
     cudaStream_t st = (cudaStream_t)stream;
@@ -669,8 +986,9 @@ int cc_seq_wkv(const CcSeqWkv* a, void* stream) {
     if (!a || !a->r || !a->k || !a->v || !a->wraw || !a->w0 || !a->u || !a->state || !a->o || a->T < 1 || a->H < 1 || a->D < 1)
         return fail(CC_SEQ_ERR_INVALID_ARG, "wkv: bad argument");
     const int P = (a->D + WKV_CH - 1) / WKV_CH;
-    if (P * WKV_J > 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "wkv: head size above 512");
-    const size_t smem = sizeof(float) * ((size_t)3 * WKV_TB * a->D + (size_t)WKV_TB * WKV_J + a->D + (size_t)WKV_TB * P * WKV_J);
+    if (P * WKV_J > 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "wkv: head size above 224");
+    const size_t smem = sizeof(float) * (2 * (size_t)WKV_TB * (3 * P * WKV_CH + WKV_J) + (size_t)WKV_TB * P * WKV_J);
+    if (smem > 200 * 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "wkv: head size above 224");
     static size_t configured = 48 * 1024;
     if (smem > configured) {
         configured = smem;
@@ -737,6 +1055,58 @@ int cc_seq_moe_expert_tokens(const void* Wgu, const void* Wd, const void* h, con
     CCM_ST(dtype, CALL);
 #undef CALL
     return cuda_check("moe_expert kernels");
+}
+
+uint64_t cc_seq_latent_decode_workspace(int32_t H, int32_t C, int32_t L) {
+    const int kpr = ld_keys_per_run(L);
+    return sizeof(float) * (uint64_t)((L + kpr - 1) / kpr) * (uint64_t)H * (2 + (uint64_t)C);
+}
+
+int cc_seq_latent_decode(const CcSeqLatentDecode* a, void* stream) {
+    if (!a || !a->q || !a->k_new || !a->k_cache || !a->pos || !a->input_pos || !a->y || a->H < 1 || a->Dk < 1 || a->C < 1 ||
+        a->C > a->Dk || a->L < 1)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "latent_decode: bad argument");
+    if (!a->workspace || a->workspace_bytes < cc_seq_latent_decode_workspace(a->H, a->C, a->L))
+        return fail(CC_SEQ_ERR_INVALID_ARG, "latent_decode: workspace missing or too small");
+    if ((size_t)(LD_HG + LD_TK) * ld_stride(a->Dk) * 4 > 200 * 1024)
+        return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "latent_decode: rows wider than 1280");
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool cb = a->cache_dtype == CC_DT_BF16, yb = a->y_dtype == CC_DT_BF16;
+    if (a->cache_dtype != CC_DT_BF16 && a->cache_dtype != CC_DT_F32) return fail(CC_SEQ_ERR_INVALID_ARG, "unknown element type");
+    if (cb && yb) return dispatch_latent_decode<bf16, bf16>(a, st);
+    if (cb && !yb) return dispatch_latent_decode<bf16, float>(a, st);
+    if (!cb && yb) return dispatch_latent_decode<float, bf16>(a, st);
+    return dispatch_latent_decode<float, float>(a, st);
+}
+
+int cc_seq_gemv_multi(const CcSeqGemvMulti* g, void* stream) {
+    if (!g || g->n_jobs < 1 || g->n_jobs > CC_GEMV_MAX_JOBS) return fail(CC_SEQ_ERR_INVALID_ARG, "gemv_multi: bad job count");
+    int blocks = 0, kmax = 0;
+    for (int j = 0; j < g->n_jobs; ++j) {
+        const CcSeqGemvJob& b = g->job[j];
+        if (!b.x || !b.W || !b.out || b.N < 1 || b.K < 1 || b.kind < CC_ACT_NONE || b.kind > CC_ACT_SIGMOID ||
+            ((b.kind != CC_ACT_NONE || b.off_up >= 0) && b.x_dtype != CC_DT_F32))
+            return fail(CC_SEQ_ERR_INVALID_ARG, "gemv_multi: bad job");
+        blocks += (b.N + 7) / 8;
+        kmax = b.K > kmax ? b.K : kmax;
+    }
+    const size_t smem = sizeof(float) * (size_t)((kmax + 3) & ~3);
+    if (smem > 200 * 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "gemv_multi: input longer than 51200");
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(ST)                                                                                                   \
+    {                                                                                                              \
+        auto kern = gemv_multi_kernel<ST>;                                                                         \
+        static size_t configured = 48 * 1024;                                                                      \
+        if (smem > configured) {                                                                                   \
+            configured = smem;                                                                                     \
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+                return cuda_check("gemv_multi: shared memory");                                                    \
+        }                                                                                                          \
+        kern<<<blocks, 256, smem, st>>>(*g);                                                                       \
+    }
+    CCM_ST(g->w_dtype, CALL);
+#undef CALL
+    return cuda_check("gemv_multi_kernel");
 }
 
 int cc_seq_moe_combine(const CcSeqMoeCombine* a, void* stream) {

@@ -34,12 +34,13 @@ from .tidelorn import _mm
 
 
 def _proj(x: Tensor, w: Tensor, one_token_kernel: bool = True) -> Tensor:
-    """x [T, K] (compute dtype) times w[N, K]^T -> fp32 [T, N]: this package's product kernel for one token, cuBLAS else."""
-    if x.shape[0] == 1 and one_token_kernel and x.is_contiguous() and w.shape[1] <= 51200:
-        out = torch.empty(1, w.shape[0], dtype=torch.float32, device=x.device)
-        seq_ops.seq_gemv(x, None, w, None, None, None, out, _lib.GEMV_PLAIN, 1.0, 0.0, 0.0, 0.0)
-        return out
+    """x [T, K] (compute dtype) times w[N, K]^T -> fp32 [T, N] through cuBLAS (prompt portions; one-token steps batch
+    their products through seq_ops.gemv_multi instead)."""
     return _mm(x, w)
+
+
+def _out(w: Tensor) -> Tensor:
+    return torch.empty(1, w.shape[0], dtype=torch.float32, device=w.device)
 
 
 def _zeros(*shape, dtype):
@@ -143,6 +144,25 @@ class WkvMixer(nn.Module):
         self.norm_w = _zeros(hd, dtype=torch.float32)
         self.w_o = _zeros(dim, hd, dtype=dtype)
 
+    def first_jobs(self, mixes: Tensor):
+        """One token: the five input products as jobs of one launch; returns (jobs, their outputs)."""
+        ws = (self.w_r, self.w_k, self.w_v, self.w_g, self.w_w1)
+        outs = [_out(w) for w in ws]
+        return [(mixes[i], w, o) for i, (w, o) in enumerate(zip(ws, outs))], outs
+
+    def finish(self, outs, state) -> Tensor:
+        """One token, after the input products: decay product (tanh applied while its input is staged), recurrence, head
+        norm and gate; returns the input of the output product."""
+        r, k, v, g, low = outs
+        H, D = self.heads, self.head_dim
+        wraw = _out(self.w_w2)
+        seq_ops.gemv_multi([(low, self.w_w2, wraw, _lib.ACT_TANH, 0, -1)])
+        o = torch.empty(1, H * D, dtype=torch.float32, device=r.device)
+        seq_ops.wkv(r, k, v, wraw, self.w0, self.u, state.matrix, o, H, D)
+        on = torch.empty(1, H * D, dtype=self.w_o.dtype, device=r.device)
+        seq_ops.head_norm_gate(o, g, self.norm_w, on, H, D, self.eps)
+        return on
+
     def forward(self, hs: Tensor, state, one_token_kernel: bool = True) -> Tensor:
         """hs fp32 [T, dim] (the shifted layer input) -> fp32 [T, dim]."""
         T, dev, dt = hs.shape[0], hs.device, self.w_r.dtype
@@ -195,37 +215,60 @@ class LatentAttention(nn.Module):
         return self.kv_rank + self.rot_dim
 
     def absorbed_fits(self) -> bool:
-        """The one-token attention kernel takes rows of up to 256 columns and up to 16 query heads per row."""
-        return self.row_width <= 256 and self.heads <= 16
+        """The one-token kernel stages 40 rows in shared memory: rows of up to 1280 columns."""
+        return self.row_width <= 1280 and self.kv_rank <= 1024
+
+    def first_jobs(self, hs_act: Tensor):
+        a = _out(self.w_in)
+        return [(hs_act, self.w_in, a)], [a]
+
+    def finish(self, outs, ip: Tensor, cache) -> Tensor:
+        """One token, absorbed form, after the down-projections: rows, query up-projection, rotation, the query through
+        W_uk^T, attention over the latent rows (the new row is stored), W_uv and the head gates on the weighted latent;
+        returns the input of the output product."""
+        (a,) = outs
+        dev, dt = a.device, self.w_in.dtype
+        H, D, R, V, C = self.heads, self.head_dim, self.rot_dim, self.v_dim, self.kv_rank
+        cq = torch.empty(1, self.q_rank, dtype=dt, device=dev)
+        krow = torch.empty(1, 1, C + R, dtype=dt, device=dev)
+        seq_ops.latent_prepare(a, 0, self.q_rank, self.q_rank, C, R, self.rot_dims, self.q_norm, self.kv_norm,
+                               self.inv_freq, ip, cq, krow, None, self.eps)
+        q = _out(self.w_uq)
+        seq_ops.gemv_multi([(cq, self.w_uq, q)])
+        qf = torch.empty(1, H, C + R, dtype=torch.float32, device=dev)
+        seq_ops.rope_heads(q, ip, self.inv_freq, H, D + R, D, R, self.rot_dims, tail=qf, tail_off=C)
+        seq_ops.head_gemv(self.w_uk_t, q, D + R, qf, C + R)
+        ctx = torch.empty(1, H, C, dtype=dt, device=dev)
+        cache.latent_step(qf, krow, ip, ctx, self.scale)
+        y = torch.empty(1, H * V, dtype=dt, device=dev)
+        seq_ops.head_gemv(self.w_ukv[H * D:].view(H, V, C), ctx, C, y, V, gate=a[0, self.q_rank + C + R:])
+        return y
 
     def forward(self, hs_act: Tensor, ip: Tensor, cache, one_token_kernel: bool = True) -> Tensor:
         T, dev, dt = hs_act.shape[0], hs_act.device, self.w_in.dtype
         H, D, R, V, C = self.heads, self.head_dim, self.rot_dim, self.v_dim, self.kv_rank
-        a = _proj(hs_act, self.w_in, one_token_kernel)
+        if T == 1 and one_token_kernel and self.absorbed_fits():
+            jobs, outs = self.first_jobs(hs_act)
+            seq_ops.gemv_multi(jobs)
+            y, out = self.finish(outs, ip, cache), _out(self.w_o)
+            seq_ops.gemv_multi([(y, self.w_o, out)])
+            return out
+        a = _proj(hs_act, self.w_in)
         cq = torch.empty(T, self.q_rank, dtype=dt, device=dev)
         krow = torch.empty(T, 1, C + R, dtype=dt, device=dev)
-        vrow = torch.empty(T, 1, C, dtype=dt, device=dev)
+        lat_new = torch.empty(T, C, dtype=dt, device=dev)     # contiguous latents for the up-projection
         seq_ops.latent_prepare(a, 0, self.q_rank, self.q_rank, C, R, self.rot_dims, self.q_norm, self.kv_norm,
-                               self.inv_freq, ip, cq, krow, vrow, self.eps)
-        q = _proj(cq, self.w_uq, one_token_kernel)                                      # fp32 [T, H * (D + R)]
+                               self.inv_freq, ip, cq, krow, lat_new, self.eps)
+        q = _proj(cq, self.w_uq)                                                        # fp32 [T, H * (D + R)]
         gate = a[:, self.q_rank + C + R:]
-        if T == 1 and one_token_kernel and self.absorbed_fits():
-            qf = torch.empty(1, H, C + R, dtype=torch.float32, device=dev)
-            seq_ops.rope_heads(q, ip, self.inv_freq, H, D + R, D, R, self.rot_dims, tail=qf, tail_off=C)
-            seq_ops.head_gemv(self.w_uk_t, q, D + R, qf, C + R)
-            ctx = torch.empty(1, H, C, dtype=dt, device=dev)
-            cache.sequence_step(qf, krow, vrow, ip, ctx, window=0, sink=None, sink_mode=_lib.SINK_NONE, scale=self.scale)
-            y = torch.empty(1, H * V, dtype=dt, device=dev)
-            seq_ops.head_gemv(self.w_ukv[H * D:].view(H, V, C), ctx, C, y, V, gate=gate.reshape(-1))
-            return _proj(y, self.w_o, one_token_kernel)
         p0 = int(ip.item())      # a prompt portion sizes its expanded rows on the host (one read per layer step)
         seq_ops.rope_heads(q, ip, self.inv_freq, H, D + R, D, R, self.rot_dims)
-        kv_new = _mm(krow.view(T, C + R)[:, :C], self.w_ukv)
+        kv_new = _mm(lat_new, self.w_ukv)
         k_new = torch.empty(T, H, D + R, dtype=dt, device=dev)
         v_new = torch.empty(T, H, V, dtype=dt, device=dev)
         if p0 > 0:
             lat_old = cache.latent_rows(p0)
-            kv_old = _mm(lat_old[:, :C], self.w_ukv)
+            kv_old = _mm(lat_old[:, :C].contiguous(), self.w_ukv)
             k_old = torch.empty(H, p0, D + R, dtype=dt, device=dev)
             v_old = torch.empty(H, p0, V, dtype=dt, device=dev)
             pos_old = cache.pos[0, 0, :p0]
@@ -234,9 +277,9 @@ class LatentAttention(nn.Module):
         seq_ops.latent_expand(kv_old, kv_new, lat_old, krow.view(T, C + R), k_old, v_old, k_new, v_new, H, D, V, R, C)
         y = torch.empty(T, H, V, dtype=dt, device=dev)
         seq_ops.attention_rows(q.view(T, H, D + R), k_new, v_new, k_old, v_old, pos_old, ip, y, self.scale)
-        cache.sequence_append(krow, vrow, ip)
+        cache.sequence_append(krow, ip)
         seq_ops.head_gate(y, gate)
-        return _proj(y.view(T, H * V), self.w_o, one_token_kernel)
+        return _proj(y.view(T, H * V), self.w_o)
 
 
 class GatedMLP(nn.Module):
@@ -253,7 +296,13 @@ class GatedMLP(nn.Module):
     def forward(self, hp: Tensor, off: int, h: Tensor, h_act: Tensor, one_token_kernel: bool = True) -> Tensor:
         act = torch.empty(hp.shape[0], self.ff, dtype=self.w_down.dtype, device=hp.device)
         seq_ops.gated_unit(hp, off, off + self.ff, act, self.act)
-        return _proj(act, self.w_down, one_token_kernel)
+        return _proj(act, self.w_down)
+
+    def one_token(self, hp: Tensor, off: int, h: Tensor, h_act: Tensor):
+        """-> (jobs for the layer's closing launch, function that returns the result after it): the gated unit is applied
+        while the down-projection stages its input."""
+        out = _out(self.w_down)
+        return [(hp, self.w_down, out, self.act, off, off + self.ff)], lambda: out
 
 
 class RoutedExperts(nn.Module):
@@ -284,24 +333,50 @@ class RoutedExperts(nn.Module):
     def n_rows(self):
         return self.n_real + self.n_identity + ((1 + 2 * self.shared_ff) if self.shared_ff else 0)
 
+    def _route(self, hp: Tensor, off: int):
+        T, dev = hp.shape[0], hp.device
+        n = self.n_real + self.n_identity
+        ids = torch.empty(T, self.top, dtype=torch.int32, device=dev)
+        wts = torch.empty(T, self.top, dtype=torch.float32, device=dev)
+        seq_ops.moe_route(hp[:, off:off + n], self.correction, ids, wts, self.groups, self.keep, self.top)
+        return ids, wts
+
+    def _few_tokens(self, h_act: Tensor, ids: Tensor):
+        M = ids.numel()
+        act = torch.empty(M, self.ff, dtype=self.w_gu.dtype, device=ids.device)
+        y = torch.empty(M, self.dim, dtype=torch.float32, device=ids.device)
+        seq_ops.moe_expert_tokens(self.w_gu, self.w_d, h_act, ids, act, y, self.act)
+        return y
+
+    def _combine(self, ids, wts, slot, y, h, shared, sg):
+        out = torch.empty(h.shape[0], self.dim, dtype=torch.float32, device=h.device)
+        seq_ops.moe_combine(ids, wts, slot, y, h, shared, sg, out, self.n_real)
+        return out
+
+    def one_token(self, hp: Tensor, off: int, h: Tensor, h_act: Tensor):
+        """-> (jobs for the layer's closing launch, function that returns the result after it)."""
+        n = self.n_real + self.n_identity
+        ids, wts = self._route(hp, off)
+        y = self._few_tokens(h_act, ids)
+        jobs, shared, sg = [], None, None
+        if self.shared_ff:
+            shared, sg = _out(self.w_shared_down), hp[:, off + n:off + n + 1]
+            jobs.append((hp, self.w_shared_down, shared, self.act, off + n + 1, off + n + 1 + self.shared_ff))
+        return jobs, lambda: self._combine(ids, wts, None, y, h, shared, sg)
+
     def forward(self, hp: Tensor, off: int, h: Tensor, h_act: Tensor, one_token_kernel: bool = True) -> Tensor:
         T, dev, dt = hp.shape[0], hp.device, self.w_gu.dtype
         n, E, F, top = self.n_real + self.n_identity, self.dim, self.ff, self.top
-        ids = torch.empty(T, top, dtype=torch.int32, device=dev)
-        wts = torch.empty(T, top, dtype=torch.float32, device=dev)
-        seq_ops.moe_route(hp[:, off:off + n], self.correction, ids, wts, self.groups, self.keep, top)
+        ids, wts = self._route(hp, off)
         shared = sg = None
         if self.shared_ff:
             sg = hp[:, off + n:off + n + 1]
             act = torch.empty(T, self.shared_ff, dtype=dt, device=dev)
             seq_ops.gated_unit(hp, off + n + 1, off + n + 1 + self.shared_ff, act, self.act)
-            shared = _proj(act, self.w_shared_down, one_token_kernel)
+            shared = _proj(act, self.w_shared_down)
         M = T * top
         if T <= self.small_t:
-            act = torch.empty(M, F, dtype=dt, device=dev)
-            y = torch.empty(M, E, dtype=torch.float32, device=dev)
-            seq_ops.moe_expert_tokens(self.w_gu, self.w_d, h_act, ids, act, y, self.act)
-            slot = None
+            y, slot = self._few_tokens(h_act, ids), None
         else:
             counts = torch.empty(self.n_real, dtype=torch.int32, device=dev)
             slot = torch.empty(M, dtype=torch.int32, device=dev)
@@ -321,9 +396,7 @@ class RoutedExperts(nn.Module):
                         seq_ops.gated_unit(gu, 0, F, act, self.act)
                         y[lo:lo + cnt] = _mm(act, self.w_d[e])
                         lo += cnt
-        out = torch.empty(T, E, dtype=torch.float32, device=dev)
-        seq_ops.moe_combine(ids, wts, slot, y, h, shared, sg, out, self.n_real)
-        return out
+        return self._combine(ids, wts, slot, y, h, shared, sg)
 
 
 # --------------------------------------------------------------------------------------------- a layer
@@ -382,6 +455,39 @@ class DetatarBlock(nn.Module):
         if self.mlp is not None:
             out.update(b=self.mlp(hp, 2 * E, h, h_act, one_token_kernel), gb=hp[:, E:2 * E], bb=self.rg2_b)
         return out
+
+
+    def step_one_token(self, x: Tensor, ip: Tensor, state, kv_cache, pending: Optional[dict]) -> dict:
+        """The same layer for one token in four kinds of launch: norm with both token shifts; all products that read the
+        normed row or its shifted copies; the mixer's core; the products that close the sublayers."""
+        E, dev, dt = x.shape[1], x.device, self.w_h.dtype
+        h = torch.empty(1, E, dtype=torch.float32, device=dev)
+        h_act = h if dt == torch.float32 else torch.empty(1, E, dtype=dt, device=dev)
+        if self.kind == "wkv":
+            shifted = torch.empty(5, 1, E, dtype=dt, device=dev)
+            shift = (state.vectors[0], self.shift.mu, None, state.vectors[1], self.mixer.shift.mu, shifted)
+        else:
+            shifted = torch.empty(1, E, dtype=dt, device=dev)
+            shift = (state.vectors[0], self.shift.mu, shifted, None, None, None)
+        seq_ops.gated_group_norm(x, self.norm1.weight, self.norm1.groups, self.norm1.eps, h, None if h_act is h else h_act,
+                                 shift=shift, **(pending or {}))
+        hp = _out(self.w_h)
+        jobs, outs = self.mixer.first_jobs(shifted)
+        seq_ops.gemv_multi([(h_act, self.w_h, hp)] + jobs)
+        core = self.mixer.finish(outs, state) if self.kind == "wkv" else self.mixer.finish(outs, ip, kv_cache)
+        mixed = _out(self.mixer.w_o)
+        closing, result = [(core, self.mixer.w_o, mixed)], None
+        if self.mlp is not None:
+            more, result = self.mlp.one_token(hp, 2 * E, h, h_act)
+            closing += more
+        seq_ops.gemv_multi(closing)
+        out = dict(a=mixed, ga=hp[:, :E], ba=self.rg1_b)
+        if result is not None:
+            out.update(b=result(), gb=hp[:, E:2 * E], bb=self.rg2_b)
+        return out
+
+    def one_token_fits(self) -> bool:
+        return self.kind == "wkv" or self.mixer.absorbed_fits()
 
 
 class DetatarLayer(nn.Module):
@@ -444,7 +550,7 @@ class DetatarTransformer(nn.Module):
             mixer = layer.block.mixer
             if layer.block.kind == "latent_attention":
                 ctor, _ = get_cache_constructor(kwargs["cache_strategy"][i])
-                layer.kv_cache = ctor(self.max_batch_size, 1, mixer.row_width, self.dtype, v_head_dim=mixer.kv_rank,
+                layer.kv_cache = ctor(self.max_batch_size, 1, mixer.row_width, self.dtype,
                                       max_cache_length=int(lengths[i]), max_seq_length=kwargs.get("max_seq_length"),
                                       global_tokens=0, cache_bits=None)
                 layer.state = state_ctor(self.max_batch_size, 0, 0, state_vectors=1, state_width=self.config.dim)
@@ -498,8 +604,12 @@ class DetatarTransformer(nn.Module):
         x = torch.empty(T, E, dtype=torch.float32, device=dev)
         seq_ops.embed_rows(tokens, self.tok_embeddings, x, self.config.embedding_scale)
         pending = None
+        one = T == 1 and fused and collect is None
         for layer in self.layers:
-            pending = layer.block(x, ip, layer.state, layer.kv_cache, pending, fused)
+            if one and layer.block.one_token_fits():
+                pending = layer.block.step_one_token(x, ip, layer.state, layer.kv_cache, pending)
+            else:
+                pending = layer.block(x, ip, layer.state, layer.kv_cache, pending, fused)
             if collect is not None:
                 apply_pending(x, pending)
                 pending = None
@@ -511,19 +621,23 @@ class DetatarTransformer(nn.Module):
         xs = torch.empty(n, E, dtype=torch.float32, device=dev)
         xs_act = xs if self.dtype == torch.float32 else torch.empty(n, E, dtype=self.dtype, device=dev)
         self.norm(x, xs, None if xs_act is xs else xs_act, pending, rows=rows)
-        return _proj(xs_act, self.output, fused).view(1, n, -1)
+        if one:
+            logits = _out(self.output)
+            seq_ops.gemv_multi([(xs_act, self.output, logits)])
+            return logits.view(1, 1, -1)
+        return _proj(xs_act, self.output).view(1, n, -1)
 
     def kernels_per_token(self) -> int:
         """Launches of this package's kernels in one decode step (fused_decode)."""
         n = 3   # embedding, last norm, output product
         for layer in self.layers:
             b = layer.block
-            n += 3      # norm, shift, fused projection of h
-            n += 13 if b.kind == "wkv" else 9
-            if isinstance(b.mlp, GatedMLP):
-                n += 2
-            elif isinstance(b.mlp, RoutedExperts):
-                n += 4 + (2 if b.mlp.shared_ff else 0)
+            n += 3      # norm with the token shifts; products of the normed row and its copies; closing products
+            # recurrent: decay product, recurrence, head norm; latent: rows, query product, rotation, 2 per-head
+            # products, attention (2 launches)
+            n += 3 if b.kind == "wkv" else 7
+            if isinstance(b.mlp, RoutedExperts):
+                n += 4      # router, experts up and down, combination
         return n
 
     # ---- weights --------------------------------------------------------------------------------

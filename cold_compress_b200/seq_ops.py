@@ -197,8 +197,11 @@ def embed_rows(tokens, embed, x, scale):
                    "cc_seq_embed_rows")
 
 
-def gated_group_norm(x, w, groups, eps, h=None, h_act=None, a=None, ga=None, ba=None, b=None, gb=None, bb=None, rows=None):
-    """x (fp32 [*, E], in place) += a * sigmoid(ga + ba) + b * sigmoid(gb + bb); h / h_act = grouped RMS norm of it."""
+def gated_group_norm(x, w, groups, eps, h=None, h_act=None, a=None, ga=None, ba=None, b=None, gb=None, bb=None, rows=None,
+                     shift=None):
+    """x (fp32 [*, E], in place) += a * sigmoid(ga + ba) + b * sigmoid(gb + bb); h / h_act = grouped RMS norm of it.
+    shift (one token only) = (state, mu, hs_act, mix_state, mix_mu, mixes): the token shift of the normed row, and a
+    second shift with several mixes on top of it, in the same launch (see cc_b200_seq.h)."""
     _need(("x", x, torch.float32), ("w", w, torch.float32), ("h", h, torch.float32), ("h_act", h_act, None),
           ("ba", ba, torch.float32), ("bb", bb, torch.float32), ("rows", rows, torch.int64))
     g = _lib.CcSeqGatedNorm()
@@ -212,6 +215,16 @@ def gated_group_norm(x, w, groups, eps, h=None, h_act=None, a=None, ga=None, ba=
     g.ba, g.bb, g.rows = _p(ba), _p(bb), _p(rows)
     g.T = rows.numel() if rows is not None else x.numel() // E
     g.E, g.groups, g.eps = E, int(groups), float(eps)
+    if shift is not None:
+        state, mu, hs_act, mix_state, mix_mu, mixes = shift
+        _need(("state", state, torch.float32), ("mu", mu, torch.float32), ("hs_act", hs_act, None), ("mix_state", mix_state, torch.float32),
+              ("mix_mu", mix_mu, torch.float32), ("mixes", mixes, None))
+        assert (hs_act is None or g.act_dtype == _dt(hs_act)) and (mixes is None or h_act is None or mixes.dtype == h_act.dtype)
+        if h_act is None and (hs_act is not None or mixes is not None):
+            g.act_dtype = _dt(hs_act if hs_act is not None else mixes)
+        g.shift_state, g.shift_mu, g.hs_act = _p(state), _p(mu), _p(hs_act)
+        g.mix_state, g.mix_mu, g.mixes = _p(mix_state), _p(mix_mu), _p(mixes)
+        g.n_mix = mix_mu.numel() // E if mix_mu is not None else 0
     _lib.check_seq(_lib.load_seq().cc_seq_gated_group_norm(C.byref(g), _stream()), "cc_seq_gated_group_norm")
 
 
@@ -349,14 +362,16 @@ def moe_combine(ids, wts, slot, y, h, shared, sg, out, n_real):
 
 
 def cache_append(k_new, v_new, k_cache, v_cache, pos, mask, cache_cts, input_pos):
-    """Rows k_new [T, G, Dk] / v_new [T, G, Dv] into slots (position mod L) of a cache, with pos / mask / cache_cts."""
+    """Rows k_new [T, G, Dk] / v_new [T, G, Dv] into slots (position mod L) of a cache, with pos / mask / cache_cts.
+    v_new = None: the cache has key rows only."""
     _need(("k_new", k_new, k_cache.dtype), ("v_new", v_new, k_cache.dtype), ("k_cache", k_cache, None), ("v_cache", v_cache, k_cache.dtype),
           ("pos", pos, torch.int32), ("mask", mask, torch.bool), ("cache_cts", cache_cts, torch.int32), ("input_pos", input_pos, torch.int32))
     a = _lib.CcSeqAttn()
-    a.k_new, a.v_new, a.k_cache, a.v_cache = _p(k_new), _p(v_new), _p(k_cache), _p(v_cache)
+    a.k_new, a.k_cache = _p(k_new), _p(k_cache)
+    a.v_new, a.v_cache = (_p(k_new), _p(k_cache)) if v_new is None else (_p(v_new), _p(v_cache))   # unused with Dv = 0
     a.pos, a.mask, a.cache_cts, a.input_pos = _p(pos), _p(mask), _p(cache_cts), _p(input_pos)
     a.T, a.G, a.Dk = k_new.shape
-    a.Dv, a.L, a.H, a.cache_dtype = v_new.shape[-1], k_cache.shape[-2], k_new.shape[1], _dt(k_cache)
+    a.Dv, a.L, a.H, a.cache_dtype = (0 if v_new is None else v_new.shape[-1]), k_cache.shape[-2], k_new.shape[1], _dt(k_cache)
     _lib.check_seq(_lib.load_seq().cc_seq_cache_append(C.byref(a), _stream()), "cc_seq_cache_append")
 
 
@@ -389,3 +404,43 @@ def _no_position(device):
     if t is None:
         t = _NO_POSITION[device] = torch.full((1,), -1, dtype=torch.int32, device=device)
     return t
+
+
+def latent_decode_workspace_bytes(H, C, L) -> int:
+    return int(_lib.load_seq().cc_seq_latent_decode_workspace(int(H), int(C), int(L)))
+
+
+def latent_decode(q, k_new, k_cache, pos, mask, cache_cts, input_pos, y, scale, workspace, append=True):
+    """Absorbed one-token latent attention: q fp32 [1, H, Dk] over rows k_cache [.., L, Dk] and k_new [.., Dk] (the newest
+    key, appended when asked); y [1, H, C] = weighted sums of the rows' first C columns."""
+    _need(("q", q, torch.float32), ("k_new", k_new, k_cache.dtype), ("k_cache", k_cache, None), ("pos", pos, torch.int32),
+          ("mask", mask, torch.bool), ("cache_cts", cache_cts, torch.int32), ("input_pos", input_pos, torch.int32), ("y", y, None),
+          ("workspace", workspace, None))
+    a = _lib.CcSeqLatentDecode()
+    a.q, a.k_new, a.k_cache, a.pos, a.mask, a.cache_cts = _p(q), _p(k_new), _p(k_cache), _p(pos), _p(mask), _p(cache_cts)
+    a.input_pos, a.y = _p(input_pos), _p(y)
+    a.H, a.Dk, a.C, a.L = q.shape[-2], q.shape[-1], y.shape[-1], k_cache.shape[-2]
+    assert k_cache.shape[-1] == a.Dk and k_new.numel() == a.Dk and y.numel() == a.H * a.C and pos.numel() == a.L
+    a.cache_dtype, a.y_dtype, a.scale, a.append = _dt(k_cache), _dt(y), float(scale), int(bool(append))
+    a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    _lib.check_seq(_lib.load_seq().cc_seq_latent_decode(C.byref(a), _stream()), "cc_seq_latent_decode")
+
+
+def gemv_multi(jobs):
+    """Up to six one-token products in one launch.  jobs: (x, w, out) or (src, w, out, kind, off_gate, off_up) where the
+    input is built from the fp32 row `src` as act(src[off_gate + k]) * src[off_up + k]; out fp32 [1, N]."""
+    g = _lib.CcSeqGemvMulti()
+    g.n_jobs = len(jobs)
+    assert 1 <= len(jobs) <= _lib.GEMV_MAX_JOBS
+    g.w_dtype = _dt(jobs[0][1])
+    for j, job in enumerate(jobs):
+        x, w, out = job[:3]
+        kind, off_gate, off_up = job[3:] if len(job) > 3 else (_lib.ACT_NONE, 0, -1)
+        _need(("x", x, None), ("w", w, jobs[0][1].dtype), ("out", out, torch.float32))
+        N, K = w.shape
+        built = kind != _lib.ACT_NONE or off_up >= 0
+        assert out.numel() == N and (x.numel() >= max(off_gate, off_up) + K if built else x.numel() == K)
+        b = g.job[j]
+        b.x, b.W, b.out = _p(x), _p(w), _p(out)
+        b.x_dtype, b.kind, b.off_gate, b.off_up, b.N, b.K = _dt(x), int(kind), int(off_gate), int(off_up), N, K
+    _lib.check_seq(_lib.load_seq().cc_seq_gemv_multi(C.byref(g), _stream()), "cc_seq_gemv_multi")

@@ -167,6 +167,10 @@ typedef struct CcSeqGatedNorm {
     const int64_t* rows;                        /* [T] or NULL */
     int32_t T, E, groups;
     float eps;
+    /* one token only (T == 1, no rows): the token shift of the normed row in the same pass.  hs = h + (shift_state - h)
+     * * shift_mu, shift_state <- h; then mixes[m] = hs + (mix_state - hs) * mix_mu[m] for m < n_mix, mix_state <- hs. */
+    float* shift_state;  const float* shift_mu;  void* hs_act;
+    float* mix_state;  const float* mix_mu;  void* mixes;  int32_t n_mix;
 } CcSeqGatedNorm;
 int cc_seq_gated_group_norm(const CcSeqGatedNorm* g, void* stream);
 
@@ -216,6 +220,41 @@ typedef struct CcSeqLatentExpand {
     int32_t dtype, n_old, n_new, H, D, V, R, kv_rank;
 } CcSeqLatentExpand;
 int cc_seq_latent_expand(const CcSeqLatentExpand* a, void* stream);
+
+/*
+ * Absorbed one-token step of latent attention: all H query heads attend over one shared row per position.
+ * q fp32 [H, Dk] (the query carried through the key up-projection | its rotated part), rows [L, Dk] in cache dtype
+ * whose first C columns are also the value row, k_new [Dk] the row of this token (position *input_pos), which is the
+ * newest key and, with `append`, is stored in slot position mod L (pos / mask / cache_cts as in CcSeqAttn).
+ * y [H, C] = softmax(scale * q . row) weighted sum of the rows' first C columns.  Keys are addressed by position.
+ */
+typedef struct CcSeqLatentDecode {
+    const float* q;  const void* k_new;  void* k_cache;
+    int32_t* pos;  uint8_t* mask;  int32_t* cache_cts;  const int32_t* input_pos;
+    void* y;
+    int32_t H, Dk, C, L, cache_dtype, y_dtype;
+    float scale;
+    int32_t append;
+    void* workspace;  uint64_t workspace_bytes;   /* cc_seq_latent_decode_workspace() bytes; needs no clearing */
+} CcSeqLatentDecode;
+uint64_t cc_seq_latent_decode_workspace(int32_t H, int32_t C, int32_t L);
+int cc_seq_latent_decode(const CcSeqLatentDecode* a, void* stream);
+
+/*
+ * Several one-token products in one launch (job j: out_j fp32 [N] = W_j [N, K] xin_j).  xin_j = x (x_dtype: fp32 or
+ * the weights' type), or, with kind != CC_ACT_NONE or off_up >= 0, built from the fp32 row x as
+ * act(x[off_gate + k]) * x[off_up + k] (no second factor when off_up < 0): the input side of a gated unit.
+ */
+#define CC_GEMV_MAX_JOBS 6
+typedef struct CcSeqGemvJob {
+    const void* x;  const void* W;  void* out;
+    int32_t x_dtype, kind, off_gate, off_up, N, K;
+} CcSeqGemvJob;
+typedef struct CcSeqGemvMulti {
+    CcSeqGemvJob job[CC_GEMV_MAX_JOBS];
+    int32_t n_jobs, w_dtype;
+} CcSeqGemvMulti;
+int cc_seq_gemv_multi(const CcSeqGemvMulti* g, void* stream);
 
 /* y [T, H, V] (dtype) *= sigmoid(g[t * ldg + h]) */
 int cc_seq_head_gate(void* y, int32_t dtype, const float* g, int64_t ldg, int32_t T, int32_t H, int32_t V, void* stream);

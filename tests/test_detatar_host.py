@@ -59,7 +59,7 @@ def test_cache_plan_and_state_sizes():
     assert ck["cache_strategy"] == ["state", "latent", "latent", "state", "latent", "latent", "state"]
     l1, l5, l0, l6 = model.layers[1], model.layers[5], model.layers[0], model.layers[6]
     assert l1.kv_cache is not l5.kv_cache and l0.state is not l6.state        # shared weights, own cache and state
-    assert l1.kv_cache.k_cache.shape == (1, 1, 64, 48) and l1.kv_cache.v_cache.shape == (1, 1, 64, 40)
+    assert l1.kv_cache.k_cache.shape == (1, 1, 64, 48) and l1.kv_cache.v_cache.numel() == 0
     assert l1.state.vectors.shape == (1, 96) and l0.state.vectors.shape == (2, 96) and l0.state.matrix.shape == (3, 24, 24)
     l0.state.matrix.fill_(1.0)
     l1.kv_cache.pos.fill_(3)
