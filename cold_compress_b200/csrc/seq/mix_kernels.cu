@@ -295,7 +295,7 @@ __global__ void __launch_bounds__(256) head_gemv_kernel(const WT* __restrict__ W
 // channels of one head; thread (part, j) keeps WKV_CH rows of column j in registers.  Tokens are staged WKV_TB at a
 // time; the parts' partial outputs meet in shared memory after each batch, summed in part order, so the arithmetic of
 // a token does not depend on how the sequence was cut into launches.
-constexpr int WKV_J = 32, WKV_CH = 16, WKV_TB = 32;
+constexpr int WKV_J = 32;   // template: TB tokens per staged batch (fewer when a wide head would not fit), CH state rows per thread
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -308,20 +308,21 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // Shared memory: two buffers of [r | k | w | v] for WKV_TB tokens (the next batch is copied in asynchronously while
 // this one is computed; rows are padded to a multiple of 4 floats so that a thread reads its 16 key channels with
 // 16-byte loads), then the parts' partial outputs.
-__global__ void wkv_kernel(const CcSeqWkv a) {
+template <int TB, int CH>
+__global__ void __launch_bounds__(512) wkv_kernel(const CcSeqWkv a) {
     extern __shared__ float4 smw4[];
     float* sm = reinterpret_cast<float*>(smw4);
-    const int D = a.D, P = (D + WKV_CH - 1) / WKV_CH, Dp = P * WKV_CH;
-    const int buf_floats = WKV_TB * (3 * Dp + WKV_J);
-    float* part = sm + 2 * buf_floats;    // [TB][P][J]
+    const int D = a.D, P = (D + CH - 1) / CH, Dp = P * CH;
+    const int buf_floats = TB * (3 * Dp + WKV_J);
+    float* __restrict__ part = sm + 2 * buf_floats;    // [TB][P][J]
     const int h = blockIdx.x, j0 = blockIdx.y * WKV_J;
     const int tid = threadIdx.x, nth = blockDim.x, jl = tid % WKV_J, p = tid / WKV_J, j = j0 + jl;
-    const int i0 = p * WKV_CH;
+    const int i0 = p * CH;
     const size_t HD = (size_t)a.H * D;
     float* S = a.state + (size_t)h * D * D;
-    float st[WKV_CH], u[WKV_CH];
+    float st[CH], u[CH];
 #pragma unroll
-    for (int c = 0; c < WKV_CH; ++c) {
+    for (int c = 0; c < CH; ++c) {
         const bool in = i0 + c < D && j < D;
         st[c] = in ? S[(size_t)(i0 + c) * D + j] : 0.f;
         u[c] = i0 + c < D ? a.u[(size_t)h * D + i0 + c] : 0.f;
@@ -329,43 +330,48 @@ __global__ void wkv_kernel(const CcSeqWkv a) {
     for (int idx = tid; idx < 2 * buf_floats; idx += nth) sm[idx] = 0.f;    // padding channels stay zero
     __syncthreads();
     auto fetch = [&](int tb, float* buf) {
-        const int nt = min(WKV_TB, a.T - tb);
-        for (int idx = tid; idx < nt * D; idx += nth) {
-            const int t = idx / D, i = idx - t * D;
-            const size_t src = (size_t)(tb + t) * HD + (size_t)h * D + i;
-            cp_async4(buf + t * Dp + i, a.r + src);
-            cp_async4(buf + WKV_TB * Dp + t * Dp + i, a.k + src);
-            cp_async4(buf + 2 * WKV_TB * Dp + t * Dp + i, a.wraw + src);
+        const int nt = min(TB, a.T - tb);
+        for (int t = 0; t < nt; ++t) {
+            const size_t row = (size_t)(tb + t) * HD + (size_t)h * D;
+            for (int i = tid; i < D; i += nth) {
+                cp_async4(buf + t * Dp + i, a.r + row + i);
+                cp_async4(buf + TB * Dp + t * Dp + i, a.k + row + i);
+                cp_async4(buf + 2 * TB * Dp + t * Dp + i, a.wraw + row + i);
+            }
         }
         for (int idx = tid; idx < nt * WKV_J; idx += nth) {
             const int t = idx / WKV_J, c = idx - t * WKV_J;
-            if (j0 + c < D) cp_async4(buf + 3 * WKV_TB * Dp + idx, a.v + (size_t)(tb + t) * HD + (size_t)h * D + j0 + c);
+            if (j0 + c < D) cp_async4(buf + 3 * TB * Dp + idx, a.v + (size_t)(tb + t) * HD + (size_t)h * D + j0 + c);
         }
         cp_async_commit();
     };
     fetch(0, sm);
     int cur = 0;
-    for (int tb = 0; tb < a.T; tb += WKV_TB, cur ^= 1) {
+    for (int tb = 0; tb < a.T; tb += TB, cur ^= 1) {
         float* buf = sm + cur * buf_floats;
-        const int nt = min(WKV_TB, a.T - tb);
-        if (tb + WKV_TB < a.T) { fetch(tb + WKV_TB, sm + (cur ^ 1) * buf_floats); cp_async_wait<1>(); }
+        const int nt = min(TB, a.T - tb);
+        if (tb + TB < a.T) { fetch(tb + TB, sm + (cur ^ 1) * buf_floats); cp_async_wait<1>(); }
         else cp_async_wait<0>();
         __syncthreads();
-        float* ws = buf + 2 * WKV_TB * Dp;
-        for (int idx = tid; idx < nt * D; idx += nth) {      // decay from its raw form, in place
-            const int t = idx / D, i = idx - t * D;
-            ws[t * Dp + i] = expf(-expf(ws[t * Dp + i] + a.w0[(size_t)h * D + i]));
+        float* ws = buf + 2 * TB * Dp;
+        for (int i = tid; i < D; i += nth) {      // decay from its raw form, in place
+            const float w0 = a.w0[(size_t)h * D + i];
+            for (int t = 0; t < nt; ++t) ws[t * Dp + i] = expf(-expf(ws[t * Dp + i] + w0));
         }
         __syncthreads();
-        const float* vs = buf + 3 * WKV_TB * Dp;
+        const float* __restrict__ vs = buf + 3 * TB * Dp;
+        const float* __restrict__ rb = buf + i0;
+        const float* __restrict__ kb = buf + TB * Dp + i0;
+        const float* __restrict__ wb = ws + i0;
+#pragma unroll 4
         for (int t = 0; t < nt; ++t) {
             const float v = vs[t * WKV_J + jl];
-            const float4* r4 = reinterpret_cast<const float4*>(buf + t * Dp + i0);
-            const float4* k4 = reinterpret_cast<const float4*>(buf + WKV_TB * Dp + t * Dp + i0);
-            const float4* w4 = reinterpret_cast<const float4*>(ws + t * Dp + i0);
+            const float4* r4 = reinterpret_cast<const float4*>(rb + t * Dp);
+            const float4* k4 = reinterpret_cast<const float4*>(kb + t * Dp);
+            const float4* w4 = reinterpret_cast<const float4*>(wb + t * Dp);
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c4 = 0; c4 < WKV_CH / 4; ++c4) {
+            for (int c4 = 0; c4 < CH / 4; ++c4) {
                 const float4 rv = r4[c4], kv4 = k4[c4], wv = w4[c4];
                 const float rr[4] = {rv.x, rv.y, rv.z, rv.w}, kk[4] = {kv4.x, kv4.y, kv4.z, kv4.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
@@ -388,7 +394,7 @@ __global__ void wkv_kernel(const CcSeqWkv a) {
         }
     }
 #pragma unroll
-    for (int c = 0; c < WKV_CH; ++c)
+    for (int c = 0; c < CH; ++c)
         if (i0 + c < D && j < D) S[(size_t)(i0 + c) * D + j] = st[c];
 }
 
@@ -845,6 +851,32 @@ __global__ void __launch_bounds__(256) gemv_multi_kernel(const CcSeqGemvMulti g)
     if (lane == 0) ((float*)jb.out)[n] = acc;
 }
 
+template <int TB, int CH>
+static int launch_wkv(const CcSeqWkv* a, cudaStream_t st) {
+    const int P = (a->D + CH - 1) / CH;
+    const size_t smem = sizeof(float) * (2 * (size_t)TB * (3 * P * CH + WKV_J) + (size_t)TB * P * WKV_J);
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        configured = smem;
+        if (cudaFuncSetAttribute(wkv_kernel<TB, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return cuda_check("wkv: shared memory");
+    }
+    dim3 grid(a->H, (a->D + WKV_J - 1) / WKV_J);
+    wkv_kernel<TB, CH><<<grid, P * WKV_J, smem, st>>>(*a);
+    return cuda_check("wkv_kernel");
+}
+
+// 8 state rows per thread up to 128-wide heads (at most 512 threads), 16 above; the token batch shrinks until two
+// staging buffers and the partial outputs fit in 160 KB.
+template <int CH>
+static int dispatch_wkv(const CcSeqWkv* a, cudaStream_t st) {
+    const int P = (a->D + CH - 1) / CH;
+    auto bytes = [&](int tb) { return sizeof(float) * (2 * (size_t)tb * (3 * P * CH + WKV_J) + (size_t)tb * P * WKV_J); };
+    if (bytes(32) <= 160 * 1024) return launch_wkv<32, CH>(a, st);
+    if (bytes(16) <= 160 * 1024) return launch_wkv<16, CH>(a, st);
+    return launch_wkv<8, CH>(a, st);
+}
+
 static int blocks_for(size_t total, int threads) {
     size_t b = (total + threads - 1) / threads;
     return (int)(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
@@ -985,19 +1017,9 @@ int cc_seq_head_gemv(const void* W, int32_t w_dtype, const void* x, int32_t x_dt
 int cc_seq_wkv(const CcSeqWkv* a, void* stream) {
     if (!a || !a->r || !a->k || !a->v || !a->wraw || !a->w0 || !a->u || !a->state || !a->o || a->T < 1 || a->H < 1 || a->D < 1)
         return fail(CC_SEQ_ERR_INVALID_ARG, "wkv: bad argument");
-    const int P = (a->D + WKV_CH - 1) / WKV_CH;
-    if (P * WKV_J > 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "wkv: head size above 224");
-    const size_t smem = sizeof(float) * (2 * (size_t)WKV_TB * (3 * P * WKV_CH + WKV_J) + (size_t)WKV_TB * P * WKV_J);
-    if (smem > 200 * 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "wkv: head size above 224");
-    static size_t configured = 48 * 1024;
-    if (smem > configured) {
-        configured = smem;
-        if (cudaFuncSetAttribute(wkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return cuda_check("wkv: shared memory");
-    }
-    dim3 grid(a->H, (a->D + WKV_J - 1) / WKV_J);
-    wkv_kernel<<<grid, P * WKV_J, smem, (cudaStream_t)stream>>>(*a);
-    return cuda_check("wkv_kernel");
+    if (a->D > 256) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "wkv: head size above 256");
+    cudaStream_t st = (cudaStream_t)stream;
+    return a->D <= 128 ? dispatch_wkv<8>(a, st) : dispatch_wkv<16>(a, st);
 }
 
 int cc_seq_head_norm_gate(const float* o, const float* graw, int64_t ldg, const float* nw, void* out, int32_t out_dtype,

@@ -80,7 +80,8 @@ def test_token_shift_kernel_carries_the_previous_row_across_portions():
     assert (torch.cat(got, 1).cpu().double() - want).abs().max() < 1e-6
 
 
-@pytest.mark.parametrize("H,D,portions", [(1, 8, (40,)), (3, 33, (1, 2, 30, 1, 17)), (2, 64, (5,) + (1,) * 20), (2, 80, (33, 16, 1))])
+@pytest.mark.parametrize("H,D,portions", [(1, 8, (40,)), (3, 33, (1, 2, 30, 1, 17)), (2, 64, (5,) + (1,) * 20), (2, 80, (33, 16, 1)),
+                                              (1, 200, (20, 1, 19)), (1, 256, (9, 1, 12))])
 def test_wkv_kernel_against_the_recurrence(H, D, portions):
     ops = _ops()
     g = torch.Generator().manual_seed(D)
