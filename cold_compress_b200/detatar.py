@@ -47,6 +47,17 @@ def _zeros(*shape, dtype):
     return nn.Parameter(torch.zeros(*shape, dtype=dtype), requires_grad=False)
 
 
+def _pad16(n: int) -> int:
+    """Rows of a fused projection are padded to a multiple of 16: the library's fast product kernels want the fp32
+    output's row stride aligned, and a router's row count (plus one gate row) is often odd."""
+    return (n + 15) // 16 * 16
+
+
+def _padded_rows(rows, total: int) -> Tensor:
+    t = torch.cat(rows)
+    return t if t.shape[0] == total else torch.cat([t, t.new_zeros(total - t.shape[0], t.shape[1])])
+
+
 # --------------------------------------------------------------------------------------------- configuration
 
 MIXERS = ("wkv", "latent_attention")
@@ -199,7 +210,7 @@ class LatentAttention(nn.Module):
             raise ValueError("rotary dims must be even and at most the rotated width")
         self.dim, self.heads, self.head_dim, self.rot_dim, self.v_dim = dim, heads, head_dim, rot_dim, v_dim
         self.q_rank, self.kv_rank, self.scale, self.rot_dims, self.eps = q_rank, kv_rank, float(scale), rot_dims, eps
-        self.w_in = _zeros(q_rank + kv_rank + rot_dim + heads, dim, dtype=dtype)       # rows: dq | dkv | g
+        self.w_in = _zeros(_pad16(q_rank + kv_rank + rot_dim + heads), dim, dtype=dtype)   # rows: dq | dkv | g | padding
         self.q_norm = _zeros(q_rank, dtype=torch.float32)
         self.kv_norm = _zeros(kv_rank, dtype=torch.float32)
         self.w_uq = _zeros(heads * (head_dim + rot_dim), q_rank, dtype=dtype)
@@ -241,7 +252,7 @@ class LatentAttention(nn.Module):
         ctx = torch.empty(1, H, C, dtype=dt, device=dev)
         cache.latent_step(qf, krow, ip, ctx, self.scale)
         y = torch.empty(1, H * V, dtype=dt, device=dev)
-        seq_ops.head_gemv(self.w_ukv[H * D:].view(H, V, C), ctx, C, y, V, gate=a[0, self.q_rank + C + R:])
+        seq_ops.head_gemv(self.w_ukv[H * D:].view(H, V, C), ctx, C, y, V, gate=a[0, self.q_rank + C + R:self.q_rank + C + R + H])
         return y
 
     def forward(self, hs_act: Tensor, ip: Tensor, cache, one_token_kernel: bool = True) -> Tensor:
@@ -260,7 +271,7 @@ class LatentAttention(nn.Module):
         seq_ops.latent_prepare(a, 0, self.q_rank, self.q_rank, C, R, self.rot_dims, self.q_norm, self.kv_norm,
                                self.inv_freq, ip, cq, krow, lat_new, self.eps)
         q = _proj(cq, self.w_uq)                                                        # fp32 [T, H * (D + R)]
-        gate = a[:, self.q_rank + C + R:]
+        gate = a[:, self.q_rank + C + R:self.q_rank + C + R + H]
         p0 = int(ip.item())      # a prompt portion sizes its expanded rows on the host (one read per layer step)
         seq_ops.rope_heads(q, ip, self.inv_freq, H, D + R, D, R, self.rot_dims)
         kv_new = _mm(lat_new, self.w_ukv)
@@ -430,7 +441,7 @@ class DetatarBlock(nn.Module):
                                      int(g.get("count", 1)), int(g.get("keep", g.get("count", 1))), int(shared.get("ff", 0)),
                                      _lib.ACT_SILU, dtype)
         n_gate = 2 * E if self.mlp is not None else E
-        self.w_h = _zeros(n_gate + (self.mlp.n_rows() if self.mlp is not None else 0), E, dtype=dtype)   # rg1 | rg2 | mlp rows
+        self.w_h = _zeros(_pad16(n_gate + (self.mlp.n_rows() if self.mlp is not None else 0)), E, dtype=dtype)   # rg1 | rg2 | mlp rows | padding
         self.rg1_b = _zeros(E, dtype=torch.float32)
         self.rg2_b = _zeros(E, dtype=torch.float32) if self.mlp is not None else None
 
@@ -687,7 +698,8 @@ class DetatarTransformer(nn.Module):
                 put(m.w_o, get(p + "mix.o", (E, hd)))
             else:
                 H, D, R, V, C = m.heads, m.head_dim, m.rot_dim, m.v_dim, m.kv_rank
-                put(m.w_in, torch.cat([get(p + "mix.dq", (m.q_rank, E)), get(p + "mix.dkv", (C + R, E)), get(p + "mix.g", (H, E))]))
+                put(m.w_in, _padded_rows([get(p + "mix.dq", (m.q_rank, E)), get(p + "mix.dkv", (C + R, E)), get(p + "mix.g", (H, E))],
+                                         m.w_in.shape[0]))
                 put(m.q_norm, get(p + "mix.dq.norm", (m.q_rank,)).float())
                 put(m.kv_norm, get(p + "mix.dkv.norm", (C,)).float())
                 put(m.w_uq, get(p + "mix.uq", (H * (D + R), m.q_rank)))
@@ -713,7 +725,7 @@ class DetatarTransformer(nn.Module):
                 put(f.w_gu, torch.stack([torch.cat([get(f"{p}mlp.e{e}.gate", (f.ff, E)), get(f"{p}mlp.e{e}.up", (f.ff, E))])
                                          for e in range(f.n_real)]))
                 put(f.w_d, torch.stack([get(f"{p}mlp.e{e}.down", (E, f.ff)) for e in range(f.n_real)]))
-            put(b.w_h, torch.cat(rows_h))
+            put(b.w_h, _padded_rows(rows_h, b.w_h.shape[0]))
         put(self.norm.weight, get("final.norm", (E,)).float())
         put(self.output, get("head", (cfg.vocab_size, E)))
         return sorted(set(tensors) - used)

@@ -25,7 +25,7 @@ def test_registry_builds_the_class_from_config(tmp_path):
     assert model.layers[0].block.mixer.w_w1.shape == (6, cfg["width"])
     b = model.layers[1].block
     assert torch.equal(b.mixer.w_uk_t[1], W["l1.mix.uk"].float().reshape(3, 16, 40)[1].T)
-    assert b.w_h.shape[0] == 2 * 96 + 8 + 1 + 2 * 40
+    assert b.w_h.shape[0] == 288 and float(b.w_h[2 * 96 + 8 + 1 + 2 * 40:].abs().sum()) == 0     # 281 rows, padded to 16
 
 
 def test_configuration_errors():

@@ -256,7 +256,9 @@ def _latent_module(dtype, H=3, D=16, Rd=8, V=24, Q=20, C=40, E=64, base=10000.0,
     W = random_weights(cfg, seed=seed)
     P = {k[len("l0.mix."):]: v for k, v in W.items() if k.startswith("l0.mix.")}
     m = LatentAttention(E, H, D, Rd, V, Q, C, cfg["layers"][0]["mixer"]["scale"], base, Rd, 1e-5, dtype)
-    m.w_in.data.copy_(torch.cat([P["dq"], P["dkv"], P["g"]]).to(dtype))
+    rows = torch.cat([P["dq"], P["dkv"], P["g"]])
+    m.w_in.data.zero_()
+    m.w_in.data[:rows.shape[0]].copy_(rows.to(dtype))
     m.q_norm.data.copy_(P["dq.norm"].float())
     m.kv_norm.data.copy_(P["dkv.norm"].float())
     m.w_uq.data.copy_(P["uq"].to(dtype))
