@@ -327,13 +327,19 @@ __global__ void __launch_bounds__(512) wkv_kernel(const CcSeqWkv a) {
         st[c] = in ? S[(size_t)(i0 + c) * D + j] : 0.f;
         u[c] = i0 + c < D ? a.u[(size_t)h * D + i0 + c] : 0.f;
     }
+    // staging layout: with more threads than channels, thread = (token lane t0, channel ich)
+    const int tstep = nth > D ? nth / D : 1, istep = nth > D ? D : nth;
+    int t0 = nth > D ? tid / D : 0;
+    const int ich = nth > D ? tid - t0 * D : tid;
+    if (t0 >= tstep) t0 = 1 << 20;      // threads beyond the last whole token lane do not stage
     for (int idx = tid; idx < 2 * buf_floats; idx += nth) sm[idx] = 0.f;    // padding channels stay zero
     __syncthreads();
     auto fetch = [&](int tb, float* buf) {
         const int nt = min(TB, a.T - tb);
-        for (int t = 0; t < nt; ++t) {
+        // thread -> (token t0 + n * tstep, channel i): every thread copies, with one division per batch
+        for (int t = t0; t < nt; t += tstep) {
             const size_t row = (size_t)(tb + t) * HD + (size_t)h * D;
-            for (int i = tid; i < D; i += nth) {
+            for (int i = ich; i < D; i += istep) {
                 cp_async4(buf + t * Dp + i, a.r + row + i);
                 cp_async4(buf + TB * Dp + t * Dp + i, a.k + row + i);
                 cp_async4(buf + 2 * TB * Dp + t * Dp + i, a.wraw + row + i);
@@ -354,9 +360,9 @@ __global__ void __launch_bounds__(512) wkv_kernel(const CcSeqWkv a) {
         else cp_async_wait<0>();
         __syncthreads();
         float* ws = buf + 2 * TB * Dp;
-        for (int i = tid; i < D; i += nth) {      // decay from its raw form, in place
+        for (int i = ich; i < D; i += istep) {      // decay from its raw form, in place
             const float w0 = a.w0[(size_t)h * D + i];
-            for (int t = 0; t < nt; ++t) ws[t * Dp + i] = expf(-expf(ws[t * Dp + i] + w0));
+            for (int t = t0; t < nt; t += tstep) ws[t * Dp + i] = expf(-expf(ws[t * Dp + i] + w0));
         }
         __syncthreads();
         const float* __restrict__ vs = buf + 3 * TB * Dp;
@@ -711,7 +717,8 @@ __global__ void __launch_bounds__(LC_WARPS * 32) latent_combine_kernel(const CcS
     extern __shared__ float smc[];          // [LC_WARPS][C + 1]
     __shared__ float red[LC_WARPS];
     const int h = blockIdx.x, C = a.C, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int p = a.input_pos[0], runs = p / ld_keys_per_run(a.L) + 1;
+    const int p = a.input_pos[0], kpr = ld_keys_per_run(a.L);
+    const int runs = min(p / kpr + 1, (a.L + kpr - 1) / kpr);   // never more runs than the tile kernel has
     const float* ws = (const float*)a.workspace;
     const size_t stride = (size_t)a.H * (2 + C);
     const float* mine = ws + (size_t)h * (2 + C);
