@@ -97,48 +97,47 @@ __global__ void embed_rows_kernel(const int32_t* __restrict__ tokens, const ST* 
 }
 
 // ------------------------------------------------------------------------------------------------ gated sum + grouped norm
-// One token per CTA: x += a * sigmoid(ga + ba) + b * sigmoid(gb + bb), then h = x / rms(x within its group) * w.
+// One (token, norm group) per CTA: x += a * sigmoid(ga + ba) + b * sigmoid(gb + bb) on the group's part of the row, then
+// h = x / rms(part) * w.  Groups are independent, so a single token still spreads over `groups` CTAs.
 template <typename ST>
 __global__ void __launch_bounds__(256) gated_group_norm_kernel(const CcSeqGatedNorm g) {
     extern __shared__ float row[];
     __shared__ float red[32];
     const int i = blockIdx.x, E = g.E, tid = threadIdx.x;
+    const int gs = E / g.groups, c0 = blockIdx.y * gs;
     const size_t t = g.rows ? (size_t)g.rows[i] : (size_t)i;
     float* x = g.x + t * E;
-    for (int e = tid; e < E; e += blockDim.x) {
-        float v = x[e];
+    float ss = 0.f;
+    for (int e = tid; e < gs; e += blockDim.x) {
+        const int c = c0 + e;
+        float v = x[c];
         if (g.a != nullptr) {
-            const float gate = g.ga ? sigmoidf_(g.ga[t * g.ldga + e] + (g.ba ? g.ba[e] : 0.f)) : 1.f;
-            v += g.a[t * g.lda + e] * gate;
+            const float gate = g.ga ? sigmoidf_(g.ga[t * g.ldga + c] + (g.ba ? g.ba[c] : 0.f)) : 1.f;
+            v += g.a[t * g.lda + c] * gate;
         }
         if (g.b != nullptr) {
-            const float gate = g.gb ? sigmoidf_(g.gb[t * g.ldgb + e] + (g.bb ? g.bb[e] : 0.f)) : 1.f;
-            v += g.b[t * g.ldb + e] * gate;
+            const float gate = g.gb ? sigmoidf_(g.gb[t * g.ldgb + c] + (g.bb ? g.bb[c] : 0.f)) : 1.f;
+            v += g.b[t * g.ldb + c] * gate;
         }
         row[e] = v;
-        if (g.a != nullptr || g.b != nullptr) x[e] = v;
+        ss += v * v;
+        if (g.a != nullptr || g.b != nullptr) x[c] = v;
     }
-    __syncthreads();
     if (g.w == nullptr) return;
-    const int gs = E / g.groups;
-    for (int grp = 0; grp < g.groups; ++grp) {
-        float ss = 0.f;
-        for (int e = tid; e < gs; e += blockDim.x) { const float v = row[grp * gs + e]; ss += v * v; }
-        const float rinv = 1.0f / sqrtf(block_sum(ss, red) / (float)gs + g.eps);
-        for (int e = tid; e < gs; e += blockDim.x) {
-            const int c = grp * gs + e;
-            const float h = row[c] * rinv * g.w[c];
-            if (g.h != nullptr) g.h[(size_t)i * E + c] = h;
-            if (g.h_act != nullptr) stf((ST*)g.h_act, (size_t)i * E + c, h);
-            if (g.shift_state != nullptr) {      // one token: its shifted copies in the same pass (thread c owns element c)
-                const float hs = h + (g.shift_state[c] - h) * g.shift_mu[c];
-                g.shift_state[c] = h;
-                if (g.hs_act != nullptr) stf((ST*)g.hs_act, c, hs);
-                if (g.n_mix > 0) {
-                    const float prev = g.mix_state[c];
-                    for (int m = 0; m < g.n_mix; ++m) stf((ST*)g.mixes, (size_t)m * E + c, hs + (prev - hs) * g.mix_mu[(size_t)m * E + c]);
-                    g.mix_state[c] = hs;
-                }
+    const float rinv = 1.0f / sqrtf(block_sum(ss, red) / (float)gs + g.eps);
+    for (int e = tid; e < gs; e += blockDim.x) {      // thread e reads back only what it wrote
+        const int c = c0 + e;
+        const float h = row[e] * rinv * g.w[c];
+        if (g.h != nullptr) g.h[(size_t)i * E + c] = h;
+        if (g.h_act != nullptr) stf((ST*)g.h_act, (size_t)i * E + c, h);
+        if (g.shift_state != nullptr) {      // one token: its shifted copies in the same pass (thread owns element c)
+            const float hs = h + (g.shift_state[c] - h) * g.shift_mu[c];
+            g.shift_state[c] = h;
+            if (g.hs_act != nullptr) stf((ST*)g.hs_act, c, hs);
+            if (g.n_mix > 0) {
+                const float prev = g.mix_state[c];
+                for (int m = 0; m < g.n_mix; ++m) stf((ST*)g.mixes, (size_t)m * E + c, hs + (prev - hs) * g.mix_mu[(size_t)m * E + c]);
+                g.mix_state[c] = hs;
             }
         }
     }
@@ -917,8 +916,8 @@ int cc_seq_gated_group_norm(const CcSeqGatedNorm* g, void* stream) {
         return fail(CC_SEQ_ERR_INVALID_ARG, "gated_group_norm: bad argument");
     if (g->shift_state && (g->T != 1 || g->rows || !g->w || !g->shift_mu || (g->n_mix > 0 && (!g->mix_state || !g->mix_mu || !g->mixes))))
         return fail(CC_SEQ_ERR_INVALID_ARG, "gated_group_norm: the fused token shift serves one token");
-    const size_t smem = sizeof(float) * (size_t)g->E;
-    if (smem > 200 * 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "gated_group_norm: rows longer than 51200");
+    const size_t smem = sizeof(float) * (size_t)(g->E / g->groups);
+    if (smem > 200 * 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "gated_group_norm: groups longer than 51200");
     cudaStream_t st = (cudaStream_t)stream;
 #define CALL(ST)                                                                                                     \
     {                                                                                                                \
@@ -929,7 +928,7 @@ int cc_seq_gated_group_norm(const CcSeqGatedNorm* g, void* stream) {
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)   \
                 return cuda_check("gated_group_norm: shared memory");                                                \
         }                                                                                                            \
-        kern<<<g->T, 256, smem, st>>>(*g);                                                                           \
+        kern<<<dim3(g->T, g->groups), 256, smem, st>>>(*g);                                                          \
     }
     CCM_ST(g->act_dtype, CALL);
 #undef CALL
