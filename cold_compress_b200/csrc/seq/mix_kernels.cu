@@ -166,12 +166,13 @@ __global__ void token_shift_kernel(const float* __restrict__ h, float* state, co
 template <typename ST>
 __global__ void gated_unit_kernel(const float* __restrict__ in, int64_t ld, int off_gate, int off_up, ST* __restrict__ out,
                                   int T, int F, int kind) {
-    const size_t total = (size_t)T * F;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t t = idx / F, f = idx - t * F;
-        float v = unit_act(in[t * ld + off_gate + f], kind);
-        if (off_up >= 0) v *= in[t * ld + off_up + f];
-        stf(out, idx, v);
+    const int f = blockIdx.x * blockDim.x + threadIdx.x;      // column; rows stride over gridDim.y (no division per element)
+    if (f >= F) return;
+    for (int t = blockIdx.y; t < T; t += gridDim.y) {
+        const float* row = in + (size_t)t * ld;
+        float v = unit_act(row[off_gate + f], kind);
+        if (off_up >= 0) v *= row[off_up + f];
+        stf(out, (size_t)t * F + f, v);
     }
 }
 
@@ -262,13 +263,14 @@ __global__ void latent_expand_kernel(const CcSeqLatentExpand a) {
     }
 }
 
-// y [T, H, V] *= sigmoid(g[t, h])
+// y [T, H, V] *= sigmoid(g[t, h]); a CTA per token
 template <typename ST>
 __global__ void head_gate_kernel(ST* __restrict__ y, const float* __restrict__ g, int64_t ldg, int T, int H, int V) {
-    const size_t total = (size_t)T * H * V;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t th = idx / V, t = th / H, h = th - t * H;
-        stf(y, idx, ldf(y, idx) * sigmoidf_(g[t * ldg + h]));
+    const size_t t = blockIdx.x;
+    for (int h = threadIdx.y; h < H; h += blockDim.y) {
+        const float gate = sigmoidf_(g[t * ldg + h]);
+        ST* row = y + (t * H + h) * V;
+        for (int v = threadIdx.x; v < V; v += blockDim.x) stf(row, v, ldf(row, v) * gate);
     }
 }
 
@@ -883,10 +885,6 @@ static int dispatch_wkv(const CcSeqWkv* a, cudaStream_t st) {
     return launch_wkv<8, CH>(a, st);
 }
 
-static int blocks_for(size_t total, int threads) {
-    size_t b = (total + threads - 1) / threads;
-    return (int)(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
-}
 
 }  // namespace ccm
 
@@ -951,7 +949,7 @@ int cc_seq_gated_unit(const float* in, int64_t ld, int32_t off_gate, int32_t off
     if (!in || !out || T < 1 || F < 1 || kind < CC_ACT_NONE || kind > CC_ACT_SIGMOID)
         return fail(CC_SEQ_ERR_INVALID_ARG, "gated_unit: bad argument");
     cudaStream_t st = (cudaStream_t)stream;
-    const int nb = blocks_for((size_t)T * F, 256);
+    const dim3 nb((F + 255) / 256, T < 4096 ? T : 4096);
 #define CALL(ST) gated_unit_kernel<ST><<<nb, 256, 0, st>>>(in, ld, off_gate, off_up, (ST*)out, T, F, kind)
     CCM_ST(out_dtype, CALL);
 #undef CALL
@@ -996,8 +994,7 @@ int cc_seq_latent_expand(const CcSeqLatentExpand* a, void* stream) {
 int cc_seq_head_gate(void* y, int32_t dtype, const float* g, int64_t ldg, int32_t T, int32_t H, int32_t V, void* stream) {
     if (!y || !g || T < 1 || H < 1 || V < 1) return fail(CC_SEQ_ERR_INVALID_ARG, "head_gate: bad argument");
     cudaStream_t st = (cudaStream_t)stream;
-    const int nb = blocks_for((size_t)T * H * V, 256);
-#define CALL(ST) head_gate_kernel<ST><<<nb, 256, 0, st>>>((ST*)y, g, ldg, T, H, V)
+#define CALL(ST) head_gate_kernel<ST><<<T, dim3(32, 8), 0, st>>>((ST*)y, g, ldg, T, H, V)
     CCM_ST(dtype, CALL);
 #undef CALL
     return cuda_check("head_gate_kernel");
