@@ -702,7 +702,7 @@ DETATAR_SIZES = {
 def _detatar_config(sz, extra):
     E = sz["width"]
     latent = {"heads": sz["heads"], "dim": 96, "rot_dim": 32, "vdim": sz["head"], "q_rank": extra["q_rank"],
-              "kv_rank": extra["kv_rank"], "scale": 128 ** -0.5, "rot": {"base": 500000.0, "dims": 32}}
+              "kv_rank": extra["kv_rank"], "scale": 128 ** -0.5, "rot": {"base": 1000000.0, "dims": 32}}
     wkv = {"heads": E // 64, "dim": 64}
     dense = {"kind": "dense", "ff": sz["ff"]}
     moe = {"kind": "moe", "expert": {"ff": extra["expert_ff"]}, "shared": {"ff": extra["shared_ff"]},

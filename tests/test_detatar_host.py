@@ -138,3 +138,40 @@ def test_restatement_identity_experts_and_rope():
     assert torch.allclose(out[..., :6].pow(2).sum(-1), v[..., :6].pow(2).sum(-1))
     a = 300 * 100.0 ** (-2 / 6)
     assert torch.allclose(out[3, 0, 1], v[3, 0, 1] * torch.cos(torch.tensor(a, dtype=torch.float64)) - v[3, 0, 4] * torch.sin(torch.tensor(a, dtype=torch.float64)))
+
+
+def test_new_entry_points_validate_their_arguments():
+    """The binding's structures line up with the header: arguments are rejected by the field they are wrong in (no launch
+    happens before validation, so this runs without a device)."""
+    import ctypes as C
+    from cold_compress_b200 import _lib
+    lib = _lib.load_seq()
+    err = lambda: lib.cc_seq_last_error().decode()
+    fake = 0x1000
+    g = _lib.CcSeqGatedNorm()
+    g.x, g.w, g.T, g.E, g.groups = fake, fake, 2, 12, 5
+    assert lib.cc_seq_gated_group_norm(C.byref(g), None) < 0 and "bad argument" in err()       # 5 groups do not divide 12
+    g.groups, g.shift_state, g.shift_mu = 3, fake, fake
+    assert lib.cc_seq_gated_group_norm(C.byref(g), None) < 0 and "one token" in err()          # the fused shift with T = 2
+    d = _lib.CcSeqLatentDecode()
+    for name in ("q", "k_new", "k_cache", "pos", "input_pos", "y"):
+        setattr(d, name, fake)
+    d.H, d.Dk, d.C, d.L = 4, 24, 32, 100
+    assert lib.cc_seq_latent_decode(C.byref(d), None) < 0 and "bad argument" in err()          # value columns beyond the row
+    d.C = 16
+    assert lib.cc_seq_latent_decode(C.byref(d), None) < 0 and "workspace" in err()
+    assert lib.cc_seq_latent_decode_workspace(4, 16, 100) == 4 * 4 * (2 + 16) * 4               # 4 runs of 32 keys
+    m = _lib.CcSeqGemvMulti()
+    assert lib.cc_seq_gemv_multi(C.byref(m), None) < 0 and "job count" in err()
+    m.n_jobs = 2
+    m.job[0].x = m.job[0].W = m.job[0].out = fake
+    m.job[0].N = m.job[0].K = 8
+    m.job[0].off_up = -1
+    assert lib.cc_seq_gemv_multi(C.byref(m), None) < 0 and "bad job" in err()                   # the second job is empty
+    w = _lib.CcSeqWkv()
+    assert lib.cc_seq_wkv(C.byref(w), None) < 0 and "wkv" in err()
+    for name in ("r", "k", "v", "wraw", "w0", "u", "state", "o"):
+        setattr(w, name, fake)
+    w.T, w.H, w.D = 1, 1, 300
+    assert lib.cc_seq_wkv(C.byref(w), None) < 0 and "256" in err()
+    assert lib.cc_seq_moe_route(fake, 8, None, fake, fake, 3, 8, 3, 1, 2, None) < 0 and "moe_route" in err()   # 3 groups of 8 outputs
