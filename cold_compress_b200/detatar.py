@@ -33,7 +33,7 @@ from .cache import get_cache_constructor
 from .tidelorn import _mm
 
 
-def _proj(x: Tensor, w: Tensor, one_token_kernel: bool = True) -> Tensor:
+def _proj(x: Tensor, w: Tensor) -> Tensor:
     """x [T, K] (compute dtype) times w[N, K]^T -> fp32 [T, N] through cuBLAS (prompt portions; one-token steps batch
     their products through seq_ops.gemv_multi instead)."""
     return _mm(x, w)
@@ -180,16 +180,16 @@ class WkvMixer(nn.Module):
         H, D = self.heads, self.head_dim
         mixes = torch.empty(5, T, self.dim, dtype=dt, device=dev)
         self.shift(hs, state.vectors[1], mixes)
-        r, k, v, g = (_proj(mixes[i], w, one_token_kernel) for i, w in enumerate((self.w_r, self.w_k, self.w_v, self.w_g)))
-        low = _proj(mixes[4], self.w_w1, one_token_kernel)
+        r, k, v, g = (_proj(mixes[i], w) for i, w in enumerate((self.w_r, self.w_k, self.w_v, self.w_g)))
+        low = _proj(mixes[4], self.w_w1)
         low_act = torch.empty(T, low.shape[1], dtype=dt, device=dev)
         seq_ops.gated_unit(low, 0, -1, low_act, _lib.ACT_TANH)
-        wraw = _proj(low_act, self.w_w2, one_token_kernel)
+        wraw = _proj(low_act, self.w_w2)
         o = torch.empty(T, H * D, dtype=torch.float32, device=dev)
         seq_ops.wkv(r, k, v, wraw, self.w0, self.u, state.matrix, o, H, D)
         on = torch.empty(T, H * D, dtype=dt, device=dev)
         seq_ops.head_norm_gate(o, g, self.norm_w, on, H, D, self.eps)
-        return _proj(on, self.w_o, one_token_kernel)
+        return _proj(on, self.w_o)
 
 
 class LatentAttention(nn.Module):
@@ -461,7 +461,7 @@ class DetatarBlock(nn.Module):
             hs_act = torch.empty(T, E, dtype=dt, device=dev)
             self.shift(h, state.vectors[0], hs_act)
             mixed = self.mixer(hs_act, ip, kv_cache, one_token_kernel)
-        hp = _proj(h_act, self.w_h, one_token_kernel)
+        hp = _proj(h_act, self.w_h)
         out = dict(a=mixed, ga=hp[:, :E], ba=self.rg1_b)
         if self.mlp is not None:
             out.update(b=self.mlp(hp, 2 * E, h, h_act, one_token_kernel), gb=hp[:, E:2 * E], bb=self.rg2_b)
