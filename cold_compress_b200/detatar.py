@@ -86,9 +86,8 @@ class DetatarArgs:
             if mlp and mlp.get("kind") not in FEED_FORWARDS:
                 raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
             j = layer.get("weights_of")
-            if j is not None and not (0 <= int(j) < i and self.layers[int(j)].get("weights_of") is None
-                                      and self.layers[int(j)]["type"] == layer["type"]):
-                raise ValueError(f"layer {i}: weights_of must name an earlier layer of the same kind with weights of its own")
+            if j is not None and not (0 <= int(j) < i and self.layers[int(j)]["type"] == layer["type"]):
+                raise ValueError(f"layer {i}: weights_of must name an earlier layer of the same kind")
 
     @classmethod
     def from_config(cls, cfg: Dict[str, Any]):

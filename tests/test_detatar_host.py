@@ -38,6 +38,9 @@ def test_configuration_errors():
         DetatarArgs.from_config(make_config([wkv_layer(None), latent_layer(None, weights_of=0)]))
     with pytest.raises(ValueError, match="groups"):
         DetatarArgs.from_config(make_config([wkv_layer(None)], width=50, groups=4))
+    # a layer may name a layer that itself borrows its weights: all three run the first one's
+    chain = DetatarTransformer.from_config(make_config([wkv_layer(None), wkv_layer(None, weights_of=0), wkv_layer(None, weights_of=1)]), torch.float32)
+    assert chain.layers[2].block is chain.layers[0].block
     cfg = make_config([wkv_layer(dense())])
     W = random_weights(cfg)
     del W["l0.mix.u"]
